@@ -1,0 +1,122 @@
+/*
+ * stof_b200 -- C ABI of the B200 (sm_100a) kernels behind the STOF operator API.
+ *
+ * Every entry point takes plain device pointers, sizes, element strides and a CUDA
+ * stream (passed as void*, a cudaStream_t; NULL = the legacy default stream).  The
+ * caller owns every buffer.  Functions return 0 on success and a negative STOF_E_*
+ * code otherwise; `stof_last_error()` then holds a message for the calling thread.
+ * Nothing here aborts the process or traps the GPU.  Kernels that wait on hardware
+ * barriers do so with a cycle budget and report through `status_dev` (a device int
+ * the caller zero-initialises; 0 = ok, otherwise (barrier id << 8) | code).
+ *
+ * "Replaces" comments cite the interface of the reference implementation
+ * (AD-pap899-SC25/SC25-STOF-AD, paths relative to its root) that an entry point stands in for.
+ */
+#ifndef STOF_B200_H
+#define STOF_B200_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define STOF_OK 0
+#define STOF_E_INVALID (-1)   /* bad argument (shape, alignment, null pointer, unsupported block size) */
+#define STOF_E_CUDA (-2)      /* a CUDA runtime / driver call failed */
+#define STOF_E_WORKSPACE (-3) /* workspace too small */
+#define STOF_E_LIMIT (-4)     /* size beyond a stated maximum */
+
+#define STOF_DTYPE_F16 0
+#define STOF_DTYPE_F32 1
+
+/* Library version (major*100 + minor) and the last error text of the calling thread. */
+int stof_version(void);
+const char* stof_last_error(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Mask -> block index compaction.
+ * Replaces: get_sparse_storage(Mask, block_size_m, block_size_n), src/util/masks.py:125-184.
+ *
+ * Two phases, because the sizes of the outputs depend on the data:
+ *   1. stof_mask_classify  : classifies every (block_m x block_n) tile of mask[0] as full / empty /
+ *      partial, counts the non-zero elements of the WHOLE (batch, S, S) tensor, and writes the
+ *      three row-pointer arrays.  `counts` (device, 4 x int64) receives
+ *      {n_full, n_part, n_load, nnz_elements}.
+ *   2. stof_mask_fill      : writes the column indices (ascending inside a row, `load` = merge of
+ *      full and partial) and gathers the partial tiles as -10000 * (1 - m) in fp16.
+ * `workspace` is scratch shared by both phases (size from stof_mask_workspace_bytes) and must stay
+ * untouched between them.  mask_dtype is STOF_DTYPE_F16 or STOF_DTYPE_F32; the mask is a dense
+ * row-major (batch, S, S) array; S must be a multiple of block_m and of block_n, block_n a multiple
+ * of 8.  Index outputs are int32.
+ * ------------------------------------------------------------------------------------------ */
+size_t stof_mask_workspace_bytes(int seq_len, int block_m, int block_n);
+
+int stof_mask_classify(const void* mask, int mask_dtype, int batch, int seq_len, int block_m, int block_n,
+                       int* full_row_ptr, int* part_row_ptr, int* load_row_ptr, /* each S/block_m + 1 */
+                       long long* counts, void* workspace, size_t workspace_bytes, void* stream);
+
+int stof_mask_fill(const void* mask, int mask_dtype, int seq_len, int block_m, int block_n,
+                   const int* full_row_ptr, const int* part_row_ptr, const int* load_row_ptr,
+                   int* full_col_idx, int* part_col_idx, int* load_col_idx,
+                   void* part_block_mask, /* fp16 (n_part, block_m, block_n); may be NULL when n_part == 0 */
+                   const void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Block-masked multi-head attention, fp16 in / fp16 out, fp32 accumulation, head_dim 64.
+ * Replaces: launch_block_attn_mask(...), src/ops/src/block_attn_mask_cuda.cu:6026-6316, as bound by
+ *           block_attn_mask_gpu, src/ops/src/block_attn_mask.cpp:17-49.
+ *
+ * For each row block only the column blocks of the full_* and part_* lists take part; a partial
+ * block adds its fp16 tile to the unscaled scores before the softmax scale, as the reference kernel
+ * does.  A row without any listed key yields zeros.  `out` may alias `q` (the reference overwrites
+ * q): every thread block reads its own query rows before it writes them.
+ * Strides are in elements for (batch, head, row); the innermost (head_dim) stride is 1.  All base
+ * pointers 16-byte aligned, strides multiples of 8 elements.  block_m in {16,32,64,128}, block_n in
+ * {16,32,64,128}; seq_len a multiple of both.  `num_warps` is accepted for signature compatibility
+ * and ignored.  load_row_ptr / load_col_idx may be NULL (they are the merge of the other two lists).
+ * ------------------------------------------------------------------------------------------ */
+int stof_block_attn(const void* q, const void* k, const void* v, void* out,
+                    int batch, int heads, int seq_len, int head_dim,
+                    const long long q_strides[3], const long long k_strides[3],
+                    const long long v_strides[3], const long long out_strides[3],
+                    const int* full_row_ptr, const int* full_col_idx,
+                    const int* part_row_ptr, const int* part_col_idx, const void* part_block_mask,
+                    const int* load_row_ptr, const int* load_col_idx,
+                    int block_m, int block_n, int num_warps, float softmax_scale,
+                    int* status_dev, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * GEMM with fused epilogue: C[M,N] = epilogue(A[M,K] @ W[K,N] + bias[N]), fp16 in/out, fp32 accumulate.
+ * Replaces: the Triton templates of src/triton_template/ (gemm_add_layernorm.py:77-144,
+ *           gemm_gemm.py:99-174) and the cuBLAS + elementwise sequences of src/benchmk_end2end.py:73-86.
+ *
+ * A row-major with row stride lda, W row-major (K rows) with row stride ldw, C row-major with row
+ * stride ldc; all in elements, multiples of 8; pointers 16-byte aligned; K, N multiples of 8.
+ * epilogue: STOF_EPI_BIAS, _GELU_ERF, _GELU_TANH, _RESIDUAL (adds residual[M,N], row stride ldr).
+ * bias may be NULL.
+ * ------------------------------------------------------------------------------------------ */
+#define STOF_EPI_BIAS 0
+#define STOF_EPI_BIAS_GELU_ERF 1
+#define STOF_EPI_BIAS_GELU_TANH 2
+#define STOF_EPI_BIAS_RESIDUAL 3
+
+int stof_gemm_bias_act(const void* a, long long lda, const void* w, long long ldw, const void* bias,
+                       const void* residual, long long ldr, void* c, long long ldc,
+                       int m, int n, int k, int epilogue, int* status_dev, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Row LayerNorm with fused bias / residual add:  y = LN(x + bias + residual) * gamma + beta.
+ * Replaces: triton_batched_bias_layernorm, src/triton_template/add_layernorm.py:19-107, and the
+ *           normalisation half of triton_matmul_bias_layernorm (gemm_add_layernorm.py:113-123).
+ * x, residual, y: (rows, hidden) fp16 with row strides in elements; bias/gamma/beta: fp16 (hidden) or
+ * NULL (0 / 1 / 0).  Statistics in fp32, biased variance.  hidden a multiple of 8, at most 8192.
+ * ------------------------------------------------------------------------------------------ */
+int stof_bias_residual_layernorm(const void* x, long long ldx, const void* bias, const void* residual, long long ldr,
+                                 const void* gamma, const void* beta, float eps, void* y, long long ldy,
+                                 int rows, int hidden, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* STOF_B200_H */

@@ -1,0 +1,261 @@
+// C[M,N] = epilogue(A[M,K] @ W[K,N] + bias) on the sm_100a tensor cores (tcgen05 + TMEM + TMA).
+//
+// Persistent kernel, one thread block per SM, 128 x 256 output tiles, K in steps of 64:
+//   warp 8      TMA producer: A tile (128 rows x 64 k, K-major) and four 64 x 64 W boxes (k rows x 64 n,
+//               i.e. N-major as the weights lie in memory) per stage, 4 stages of 48 KB
+//   warp 9      MMA issuer: 4 tcgen05.mma (128 x 256 x 16) per stage into one of two 256-column fp32
+//               accumulators in tensor memory; tcgen05.commit releases the stage / publishes the tile
+//   warps 0-7   epilogue: tcgen05.ld 32 columns at a time, + bias, optional GELU (erf or tanh form) or
+//               + residual, fp16 pack, 128-bit stores; runs under the next tile's main loop
+// Weights are consumed in their (K, N) row-major layout through an MN-major shared-memory
+// descriptor, so no transposed copy is ever made.
+#include "stof_host.h"
+#include "stof_ptx.cuh"
+
+namespace stof {
+namespace {
+
+constexpr int G_BM = 128, G_BN = 256, G_BK = 64;
+constexpr int G_STAGES = 4;
+constexpr int G_A_BYTES = G_BM * G_BK * 2;            // 16 KB
+constexpr int G_B_BYTES = G_BK * G_BN * 2;            // 32 KB
+constexpr int G_STAGE_BYTES = G_A_BYTES + G_B_BYTES;  // 48 KB
+constexpr int G_EPI_WARPS = 8;
+constexpr int G_THREADS = (G_EPI_WARPS + 2) * 32;
+constexpr int G_TMEM_COLS = 512;
+constexpr size_t G_SMEM = 1024 + static_cast<size_t>(G_STAGES) * G_STAGE_BYTES + 256;
+
+enum { BAR_FULL = 0, BAR_EMPTY = G_STAGES, BAR_TFULL = 2 * G_STAGES, BAR_TEMPTY = 2 * G_STAGES + 2, BAR_COUNT = 2 * G_STAGES + 4 };
+
+__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
+__device__ __forceinline__ float gelu_tanh(float x) {
+    const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+    return 0.5f * x * (1.0f + tanhf(u));
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(G_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const __half* __restrict__ bias,
+            const __half* __restrict__ residual, long long ldr, __half* __restrict__ c, long long ldc, int m, int n, int k,
+            int* status) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + G_STAGES * G_STAGE_BYTES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + BAR_COUNT);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_n = (n + G_BN - 1) / G_BN, tiles_m = (m + G_BM - 1) / G_BM;
+    const int num_tiles = tiles_m * tiles_n;
+    const int kblocks = (k + G_BK - 1) / G_BK;
+    const WaitCtx wctx{abort_flag, status};
+
+    if (threadIdx.x == 0) {
+        *abort_flag = (status != nullptr && *status != 0) ? 1 : 0;
+        for (int i = 0; i < G_STAGES; ++i) {
+            mbar_init(&bars[BAR_FULL + i], 1);
+            mbar_init(&bars[BAR_EMPTY + i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bars[BAR_TFULL + i], 1);
+            mbar_init(&bars[BAR_TEMPTY + i], G_EPI_WARPS);
+        }
+        fence_mbar_init();
+    }
+    if (warp == G_EPI_WARPS + 1) {
+        tmem_alloc(tmem_slot, G_TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (*abort_flag == 0) {
+        if (warp == G_EPI_WARPS) {
+            // ------------------------------------------------------------------ TMA producer
+            if (elect_one()) {
+                tma_prefetch_desc(&map_a);
+                tma_prefetch_desc(&map_w);
+                int it = 0;
+                for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+                    const int m0 = (t / tiles_n) * G_BM, n0 = (t % tiles_n) * G_BN;
+                    for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                        const int s = it % G_STAGES;
+                        const uint32_t ph = (it / G_STAGES) & 1;
+                        mbar_wait(&bars[BAR_EMPTY + s], ph ^ 1, wctx, BAR_EMPTY + s);
+                        unsigned char* a_dst = smem + s * G_STAGE_BYTES;
+                        unsigned char* b_dst = a_dst + G_A_BYTES;
+                        mbar_arrive_expect_tx(&bars[BAR_FULL + s], G_STAGE_BYTES);
+                        tma_load_2d(a_dst, &map_a, &bars[BAR_FULL + s], kb * G_BK, m0);
+#pragma unroll
+                        for (int j = 0; j < G_BN / 64; ++j)
+                            tma_load_2d(b_dst + j * (G_BK * 64 * 2), &map_w, &bars[BAR_FULL + s], n0 + 64 * j, kb * G_BK);
+                    }
+                }
+            }
+        } else if (warp == G_EPI_WARPS + 1) {
+            // ------------------------------------------------------------------ MMA issuer
+            if (elect_one()) {
+                constexpr uint32_t idesc = make_idesc_f16(G_BM, G_BN, /*b_mn_major=*/true);
+                int it = 0, local = 0;
+                for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++local) {
+                    const int acc = local & 1;
+                    const uint32_t acc_ph = (local >> 1) & 1;
+                    mbar_wait(&bars[BAR_TEMPTY + acc], acc_ph ^ 1, wctx, BAR_TEMPTY + acc);
+                    tc_fence_after();
+                    const uint32_t d_tmem = tmem_base + acc * G_BN;
+                    for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                        const int s = it % G_STAGES;
+                        const uint32_t ph = (it / G_STAGES) & 1;
+                        mbar_wait(&bars[BAR_FULL + s], ph, wctx, BAR_FULL + s);
+                        tc_fence_after();
+                        const uint32_t a_addr = smem_u32(smem + s * G_STAGE_BYTES);
+                        const uint32_t b_addr = a_addr + G_A_BYTES;
+#pragma unroll
+                        for (int kk = 0; kk < G_BK / 16; ++kk) {
+                            const uint64_t a_desc = make_smem_desc_sw128(a_addr + kk * 32, 16, 1024);
+                            const uint64_t b_desc = make_smem_desc_sw128(b_addr + kk * 2048, G_BK * 64 * 2, 1024);
+                            mma_f16_ss(d_tmem, a_desc, b_desc, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                        }
+                        tc_commit(&bars[BAR_EMPTY + s]);
+                    }
+                    tc_commit(&bars[BAR_TFULL + acc]);
+                }
+            }
+        } else {
+            // ------------------------------------------------------------------ epilogue
+            const int quarter = warp & 3, half_n = warp >> 2;
+            int local = 0;
+            for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++local) {
+                const int acc = local & 1;
+                const uint32_t acc_ph = (local >> 1) & 1;
+                const int m0 = (t / tiles_n) * G_BM, n0 = (t % tiles_n) * G_BN;
+                mbar_wait(&bars[BAR_TFULL + acc], acc_ph, wctx, BAR_TFULL + acc);
+                tc_fence_after();
+                const int row = m0 + quarter * 32 + lane;
+                const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * G_BN + half_n * (G_BN / 2);
+#pragma unroll 1
+                for (int ch = 0; ch < G_BN / 2 / 32; ++ch) {
+                    uint32_t r[32];
+                    tmem_ld32(t_row + ch * 32, r);
+                    tc_wait_ld();
+                    const int col0 = n0 + half_n * (G_BN / 2) + ch * 32;
+                    if (row < m && col0 < n) {
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            const int col = col0 + 8 * g;
+                            if (col < n) {
+                                float v[8];
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[8 * g + j]);
+                                if (bias) {
+                                    const uint4 bu = __ldg(reinterpret_cast<const uint4*>(bias + col));
+                                    const __half2* bh = reinterpret_cast<const __half2*>(&bu);
+#pragma unroll
+                                    for (int j = 0; j < 4; ++j) {
+                                        const float2 f = __half22float2(bh[j]);
+                                        v[2 * j] += f.x;
+                                        v[2 * j + 1] += f.y;
+                                    }
+                                }
+                                if (EPI == STOF_EPI_BIAS_GELU_ERF) {
+#pragma unroll
+                                    for (int j = 0; j < 8; ++j) v[j] = gelu_erf(v[j]);
+                                } else if (EPI == STOF_EPI_BIAS_GELU_TANH) {
+#pragma unroll
+                                    for (int j = 0; j < 8; ++j) v[j] = gelu_tanh(v[j]);
+                                } else if (EPI == STOF_EPI_BIAS_RESIDUAL) {
+                                    const uint4 ru = __ldg(reinterpret_cast<const uint4*>(residual + static_cast<size_t>(row) * ldr + col));
+                                    const __half2* rh = reinterpret_cast<const __half2*>(&ru);
+#pragma unroll
+                                    for (int j = 0; j < 4; ++j) {
+                                        const float2 f = __half22float2(rh[j]);
+                                        v[2 * j] += f.x;
+                                        v[2 * j + 1] += f.y;
+                                    }
+                                }
+                                uint4 o;
+                                o.x = pack_half2(v[0], v[1]);
+                                o.y = pack_half2(v[2], v[3]);
+                                o.z = pack_half2(v[4], v[5]);
+                                o.w = pack_half2(v[6], v[7]);
+                                *reinterpret_cast<uint4*>(c + static_cast<size_t>(row) * ldc + col) = o;
+                            }
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars[BAR_TEMPTY + acc]);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == G_EPI_WARPS + 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, G_TMEM_COLS);
+    }
+}
+
+template <int EPI>
+int launch(const CUtensorMap& ma, const CUtensorMap& mw, const __half* bias, const __half* residual, long long ldr, __half* c, long long ldc,
+           int m, int n, int k, int* status, cudaStream_t stream) {
+    static bool configured[64] = {};
+    int dev = 0;
+    STOF_CUDA(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        STOF_CUDA(cudaFuncSetAttribute(gemm_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(G_SMEM)));
+        configured[dev] = true;
+    }
+    const int tiles = ((m + G_BM - 1) / G_BM) * ((n + G_BN - 1) / G_BN);
+    int grid = sm_count();
+    if (grid > tiles) grid = tiles;
+    gemm_kernel<EPI><<<grid, G_THREADS, G_SMEM, stream>>>(ma, mw, bias, residual, ldr, c, ldc, m, n, k, status);
+    STOF_CUDA(cudaGetLastError());
+    return STOF_OK;
+}
+
+}  // namespace
+}  // namespace stof
+
+using namespace stof;
+
+extern "C" int stof_gemm_bias_act(const void* a, long long lda, const void* w, long long ldw, const void* bias, const void* residual,
+                                  long long ldr, void* c, long long ldc, int m, int n, int k, int epilogue, int* status_dev,
+                                  void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    STOF_REQUIRE(a && w && c, "gemm: null operand");
+    STOF_REQUIRE(m >= 0 && n > 0 && k > 0, "gemm: bad shape m=%d n=%d k=%d", m, n, k);
+    STOF_REQUIRE(n % 8 == 0 && k % 8 == 0, "gemm: n=%d and k=%d must be multiples of 8", n, k);
+    STOF_REQUIRE(lda % 8 == 0 && ldw % 8 == 0 && ldc % 8 == 0, "gemm: leading dimensions must be multiples of 8 elements");
+    STOF_REQUIRE(lda >= k && ldw >= n && ldc >= n, "gemm: leading dimension smaller than the row length");
+    STOF_REQUIRE(aligned16(a) && aligned16(w) && aligned16(c) && aligned16(bias) && aligned16(residual), "gemm: pointers must be 16-byte aligned");
+    STOF_REQUIRE(epilogue >= STOF_EPI_BIAS && epilogue <= STOF_EPI_BIAS_RESIDUAL, "gemm: unknown epilogue %d", epilogue);
+    if (epilogue == STOF_EPI_BIAS_RESIDUAL)
+        STOF_REQUIRE(residual && ldr % 8 == 0 && ldr >= n, "gemm: residual epilogue needs a residual with a row stride multiple of 8, >= n");
+    if (m == 0) return STOF_OK;
+
+    CUtensorMap ma, mw;
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(m)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(lda) * 2};
+        const uint32_t box[2] = {G_BK, G_BM};
+        if (int rc = make_tensor_map_f16(&ma, a, 2, dims, strides, box)) return rc;
+    }
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(n), static_cast<uint64_t>(k)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(ldw) * 2};
+        const uint32_t box[2] = {64, G_BK};
+        if (int rc = make_tensor_map_f16(&mw, w, 2, dims, strides, box)) return rc;
+    }
+    const __half *bp = static_cast<const __half*>(bias), *rp = static_cast<const __half*>(residual);
+    __half* cp = static_cast<__half*>(c);
+    switch (epilogue) {
+        case STOF_EPI_BIAS: return launch<STOF_EPI_BIAS>(ma, mw, bp, rp, ldr, cp, ldc, m, n, k, status_dev, stream);
+        case STOF_EPI_BIAS_GELU_ERF: return launch<STOF_EPI_BIAS_GELU_ERF>(ma, mw, bp, rp, ldr, cp, ldc, m, n, k, status_dev, stream);
+        case STOF_EPI_BIAS_GELU_TANH: return launch<STOF_EPI_BIAS_GELU_TANH>(ma, mw, bp, rp, ldr, cp, ldc, m, n, k, status_dev, stream);
+        default: return launch<STOF_EPI_BIAS_RESIDUAL>(ma, mw, bp, rp, ldr, cp, ldc, m, n, k, status_dev, stream);
+    }
+}

@@ -1,0 +1,186 @@
+// y = LayerNorm(x + bias + residual) * gamma + beta over rows of fp16, fp32 statistics (HBM-bound).
+//
+// One warp per row.  The row is read once with 128-bit loads, held in registers as fp32, reduced
+// with warp shuffles (mean, then the centred sum of squares, biased variance as
+// src/triton_template/add_layernorm.py:33-55 and F.layer_norm do), and written once with 128-bit
+// stores.  Rows longer than 2048 elements are re-read from cache for the second and third sweep
+// instead of being held in registers.
+#include "stof_host.h"
+
+#include <cuda_fp16.h>
+
+namespace stof {
+namespace {
+
+constexpr int LN_WARPS = 8;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ void load8(const __half* p, float (&f)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 t = __half22float2(h[i]);
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+
+__device__ __forceinline__ void add8(const __half* p, float (&f)[8]) {
+    float t[8];
+    load8(p, t);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] += t[i];
+}
+
+__device__ __forceinline__ void store8(__half* p, const float (&f)[8]) {
+    uint4 u;
+    __half2* h = reinterpret_cast<__half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = u;
+}
+
+// NCHUNK: 16-byte chunks held per lane (hidden <= NCHUNK * 256); NCHUNK == 0 selects the re-reading variant.
+template <int NCHUNK>
+__global__ void __launch_bounds__(LN_WARPS * 32)
+layernorm_kernel(const __half* x, long long ldx, const __half* __restrict__ bias, const __half* __restrict__ residual,
+                 long long ldr, const __half* __restrict__ gamma, const __half* __restrict__ beta, float eps, __half* y,
+                 long long ldy, int rows, int hidden) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * LN_WARPS + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const __half* xr = x + static_cast<size_t>(row) * ldx;
+    const __half* rr = residual ? residual + static_cast<size_t>(row) * ldr : nullptr;
+    __half* yr = y + static_cast<size_t>(row) * ldy;
+    const int nchunks = hidden >> 3;
+    const float inv_n = 1.0f / static_cast<float>(hidden);
+
+    if constexpr (NCHUNK > 0) {
+        float v[NCHUNK][8];
+        float sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < NCHUNK; ++i) {
+            const int c = lane + 32 * i;
+            if (c < nchunks) {
+                load8(xr + 8 * c, v[i]);
+                if (bias) add8(bias + 8 * c, v[i]);
+                if (rr) add8(rr + 8 * c, v[i]);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) sum += v[i][j];
+            }
+        }
+        const float mean = warp_sum(sum) * inv_n;
+        float sq = 0.f;
+#pragma unroll
+        for (int i = 0; i < NCHUNK; ++i) {
+            if (lane + 32 * i < nchunks) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float d = v[i][j] - mean;
+                    sq += d * d;
+                }
+            }
+        }
+        const float rstd = 1.0f / sqrtf(warp_sum(sq) * inv_n + eps);
+#pragma unroll
+        for (int i = 0; i < NCHUNK; ++i) {
+            const int c = lane + 32 * i;
+            if (c < nchunks) {
+                float g[8], b[8];
+                if (gamma) load8(gamma + 8 * c, g);
+                if (beta) load8(beta + 8 * c, b);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    float o = (v[i][j] - mean) * rstd;
+                    if (gamma) o *= g[j];
+                    if (beta) o += b[j];
+                    v[i][j] = o;
+                }
+                store8(yr + 8 * c, v[i]);
+            }
+        }
+    } else {
+        float sum = 0.f;
+        for (int c = lane; c < nchunks; c += 32) {
+            float t[8];
+            load8(xr + 8 * c, t);
+            if (bias) add8(bias + 8 * c, t);
+            if (rr) add8(rr + 8 * c, t);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sum += t[j];
+        }
+        const float mean = warp_sum(sum) * inv_n;
+        float sq = 0.f;
+        for (int c = lane; c < nchunks; c += 32) {
+            float t[8];
+            load8(xr + 8 * c, t);
+            if (bias) add8(bias + 8 * c, t);
+            if (rr) add8(rr + 8 * c, t);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float d = t[j] - mean;
+                sq += d * d;
+            }
+        }
+        const float rstd = 1.0f / sqrtf(warp_sum(sq) * inv_n + eps);
+        for (int c = lane; c < nchunks; c += 32) {
+            float t[8], g[8], b[8];
+            load8(xr + 8 * c, t);
+            if (bias) add8(bias + 8 * c, t);
+            if (rr) add8(rr + 8 * c, t);
+            if (gamma) load8(gamma + 8 * c, g);
+            if (beta) load8(beta + 8 * c, b);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                float o = (t[j] - mean) * rstd;
+                if (gamma) o *= g[j];
+                if (beta) o += b[j];
+                t[j] = o;
+            }
+            store8(yr + 8 * c, t);
+        }
+    }
+}
+
+}  // namespace
+}  // namespace stof
+
+using namespace stof;
+
+extern "C" int stof_bias_residual_layernorm(const void* x, long long ldx, const void* bias, const void* residual, long long ldr,
+                                            const void* gamma, const void* beta, float eps, void* y, long long ldy, int rows, int hidden,
+                                            void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    STOF_REQUIRE(x && y, "layernorm: null x or y");
+    STOF_REQUIRE(rows >= 0 && hidden > 0, "layernorm: bad shape (%d, %d)", rows, hidden);
+    STOF_REQUIRE(hidden % 8 == 0, "layernorm: hidden %d must be a multiple of 8", hidden);
+    if (hidden > 8192) {
+        set_error("layernorm: hidden %d beyond the maximum of 8192", hidden);
+        return STOF_E_LIMIT;
+    }
+    STOF_REQUIRE(ldx % 8 == 0 && ldy % 8 == 0 && (!residual || ldr % 8 == 0), "layernorm: row strides must be multiples of 8 elements");
+    STOF_REQUIRE(ldx >= hidden && ldy >= hidden && (!residual || ldr >= hidden), "layernorm: row stride smaller than hidden");
+    STOF_REQUIRE(aligned16(x) && aligned16(y) && aligned16(bias) && aligned16(residual) && aligned16(gamma) && aligned16(beta),
+                 "layernorm: pointers must be 16-byte aligned");
+    if (rows == 0) return STOF_OK;
+    const dim3 grid((rows + LN_WARPS - 1) / LN_WARPS), block(LN_WARPS * 32);
+    const __half *xp = static_cast<const __half*>(x), *bp = static_cast<const __half*>(bias), *rp = static_cast<const __half*>(residual),
+                 *gp = static_cast<const __half*>(gamma), *tp = static_cast<const __half*>(beta);
+    __half* yp = static_cast<__half*>(y);
+#define STOF_LN_LAUNCH(N) layernorm_kernel<N><<<grid, block, 0, stream>>>(xp, ldx, bp, rp, ldr, gp, tp, eps, yp, ldy, rows, hidden)
+    if (hidden <= 256) STOF_LN_LAUNCH(1);
+    else if (hidden <= 512) STOF_LN_LAUNCH(2);
+    else if (hidden <= 768) STOF_LN_LAUNCH(3);
+    else if (hidden <= 1024) STOF_LN_LAUNCH(4);
+    else if (hidden <= 2048) STOF_LN_LAUNCH(8);
+    else STOF_LN_LAUNCH(0);
+#undef STOF_LN_LAUNCH
+    STOF_CUDA(cudaGetLastError());
+    return STOF_OK;
+}

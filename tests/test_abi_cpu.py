@@ -1,0 +1,123 @@
+"""CPU-side checks: the C-ABI library loads and exports what the header declares, argument validation
+answers without a GPU, and the host-side generators reproduce the reference's masks."""
+import ctypes
+import hashlib
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def built_lib():
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("stof_build", os.path.join(ROOT, "sc25-stof-ad_b200", "build.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    path = mod.build_library()
+    from stof_b200 import _lib
+    return _lib.lib(), path
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "stof_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(stof_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(built_lib):
+    L, path = built_lib
+    names = declared_symbols()
+    assert len(names) >= 8
+    raw = ctypes.CDLL(path)
+    for n in names:
+        assert hasattr(raw, n), f"{n} declared in include/stof_b200.h but not exported"
+    assert L.stof_version() >= 100
+
+
+def test_binding_table_matches_header(built_lib):
+    from stof_b200 import _lib
+    assert sorted(_lib.EXPORTS) == declared_symbols()
+
+
+def test_argument_validation_needs_no_gpu(built_lib):
+    L, _ = built_lib
+    from stof_b200 import _lib
+    s3 = _lib.strides3((64, 64, 64))
+    one = ctypes.c_void_p(16)
+    rc = L.stof_block_attn(one, one, one, one, 1, 1, 64, 32, s3, s3, s3, s3, one, one, one, one, None, None, None, 64, 64, 4, 0.125, None, None)
+    assert rc == -1 and b"head_dim" in L.stof_last_error()
+    rc = L.stof_block_attn(one, one, one, one, 1, 1, 100, 64, s3, s3, s3, s3, one, one, one, one, None, None, None, 64, 64, 4, 0.125, None, None)
+    assert rc == -1 and b"multiple" in L.stof_last_error()
+    rc = L.stof_block_attn(one, one, one, one, 1, 1, 96, 64, s3, s3, s3, s3, one, one, one, one, None, None, None, 48, 48, 4, 0.125, None, None)
+    assert rc == -1 and b"BLOCK_M" in L.stof_last_error()
+    rc = L.stof_mask_classify(one, 0, 1, 100, 64, 64, one, one, one, one, one, 1 << 20, None)
+    assert rc == -1
+    rc = L.stof_mask_classify(one, 0, 1, 128, 64, 64, one, one, one, one, one, 8, None)
+    assert rc == -3 and b"workspace" in L.stof_last_error()
+    rc = L.stof_gemm_bias_act(one, 60, one, 64, None, None, 0, one, 64, 8, 64, 60, 0, None, None)
+    assert rc == -1
+    rc = L.stof_bias_residual_layernorm(one, 16384, None, None, 0, None, None, 1e-5, one, 16384, 4, 16384, None)
+    assert rc == -4 and b"8192" in L.stof_last_error()
+    assert L.stof_mask_workspace_bytes(4096, 64, 64) == 16 + 64 * 64
+
+
+def test_ops_refuse_cpu_tensors(built_lib):
+    import stof_b200
+    x = torch.zeros(2, 8, dtype=torch.float16)
+    with pytest.raises(stof_b200.StofError):
+        stof_b200.bias_residual_layernorm(x)
+    with pytest.raises(stof_b200.StofError):
+        stof_b200.gemm_bias(x, torch.zeros(8, 8, dtype=torch.float16))
+
+
+def test_host_generators_match_reference_masks():
+    from _cases import golden_meta
+    import stof_b200.masks as hm
+    meta = golden_meta()
+
+    def sha(t):
+        return hashlib.sha256(np.ascontiguousarray(t.numpy()).tobytes()).hexdigest()
+
+    z = lambda b, s: torch.zeros(b, s, s, dtype=torch.float16)
+    assert sha(hm.generate_sliding_mask(z(1, 256), bandwidth=32)) == meta["sliding_bw32_S256_b64"]["mask_sha256"]
+    assert sha(hm.generate_causal_mask(z(1, 256))) == meta["causal_S256_b32"]["mask_sha256"]
+    assert sha(hm.generate_bigbird_mask(z(1, 512), globalwidth=32, bandwidth=32, fill_rate=0.2)) == meta["bigbird_S512_b32"]["mask_sha256"]
+    assert sha(hm.generate_bigbird_mask(z(1, 512), globalwidth=1, bandwidth=1, fill_rate=0.2)) == meta["bigbird_S512_b64"]["mask_sha256"]
+    assert sha(hm.generate_longformer_mask(z(1, 512), globalwidth=16, bandwidth=48)) == meta["longformer_S512_b64"]["mask_sha256"]
+    assert sha(hm.generate_dilated_mask(z(1, 256), bandwidth=8, dilation_rate=1)) == meta["dilated_S256_b16"]["mask_sha256"]
+    assert sha(hm.generate_sliding_mask(z(2, 128), bandwidth=20, is_cauasl=True)) == meta["sliding_causal_B2_S128_b32"]["mask_sha256"]
+
+
+def test_drop_in_module_names_import():
+    import ops.package_op as po
+    import util.masks as um
+    import util.utils as uu
+    import triton_template.gemm_add_layernorm as t1
+    import triton_template.gemm_gemm as t2
+    import triton_template.add_layernorm as t3
+    import block_attn_mask as ext
+    assert callable(po.block_attn_mask_op) and callable(ext.forward)
+    assert callable(um.get_sparse_storage) and callable(um.generate_bigbird_mask)
+    assert callable(uu.transpose_for_scores) and callable(uu.time_stamp_cudasync)
+    assert callable(t1.triton_matmul_bias_layernorm) and callable(t2.triton_matmul_batch) and callable(t3.triton_batched_bias_layernorm)
+    x = torch.arange(2 * 4 * 6.0).view(2, 4, 6)
+    assert uu.transpose_for_scores(x, 2, 3).shape == (2, 2, 4, 3)
+
+
+def test_workload_recipes_equal_the_oracle_recipes():
+    from oracle import masks as om
+    from stof_b200 import workloads as wl
+    pairs = {"cfg1": "cfg1_sliding_S256", "cfg2": "cfg2_bigbird_S2048_seed1", "cfg3": "cfg3_longdil_S4096"}
+    for key, oname in pairs.items():
+        assert np.array_equal(wl.config_mask(wl.ATTENTION_CONFIGS[key]).numpy(), om.recipe_mask(oname)), key
+    for key, oname in {"cfg4": "cfg4_sliding2_S1024", "cfg5": "cfg5_bigbird_S4096_seed4"}.items():
+        assert np.array_equal(wl.config_mask(wl.ENCODER_CONFIGS[key]).numpy(), om.recipe_mask(oname)), key
+    q, k, v = wl.attention_inputs(wl.ATTENTION_CONFIGS["cfg1"])
+    g = torch.Generator().manual_seed(0)
+    assert torch.equal(q, torch.randn(1, 12, 256, 64, generator=g).half())
+    assert wl.attention_flops(286, 16, 12) == pytest.approx(5.758e10, rel=1e-3)

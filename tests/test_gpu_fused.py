@@ -1,0 +1,120 @@
+"""tcgen05 GEMM epilogues, LayerNorm and the encoder layer against the CPU oracle."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import fused as of
+from oracle import masks as om
+from _cases import GOLDEN
+
+pytestmark = pytest.mark.gpu
+
+
+def _rand(shape, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).half()
+
+
+def _err(a, b):
+    return (a.float().cpu() - b).abs().max().item()
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (256, 512, 128), (300, 264, 200), (1000, 768, 768), (64, 3072, 768), (2048, 1024, 4096), (1, 8, 8)])
+def test_gemm_bias_matches_oracle(m, n, k):
+    import stof_b200
+    a, w, b = _rand((m, k), 1), _rand((k, n), 2, 0.05), _rand((n,), 3)
+    got = stof_b200.gemm_bias(a.cuda(), w.cuda(), b.cuda())
+    torch.cuda.synchronize()
+    want = of.gemm_bias(a, w, b)
+    # fp32 accumulation, one fp16 rounding of the result: half an ulp of the largest magnitude plus summation noise
+    tol = 2e-3 * max(1.0, want.abs().max().item())
+    assert _err(got, want) <= tol
+
+
+@pytest.mark.parametrize("mode", ["erf", "tanh"])
+def test_gemm_bias_gelu(mode):
+    import stof_b200
+    a, w, b = _rand((512, 256), 4), _rand((256, 1024), 5, 0.1), _rand((1024,), 6)
+    got = stof_b200.gemm_bias_gelu(a.cuda(), w.cuda(), b.cuda(), mode)
+    torch.cuda.synchronize()
+    want = of.gemm_bias_gelu(a, w, b, mode)
+    assert _err(got, want) <= 2e-3 * max(1.0, want.abs().max().item())
+
+
+def test_gemm_bias_residual_and_3d_inputs():
+    import stof_b200
+    a, w, b, r = _rand((4, 96, 128), 7), _rand((128, 256), 8, 0.1), _rand((256,), 9), _rand((4, 96, 256), 10)
+    got = stof_b200.gemm_bias_residual(a.cuda(), w.cuda(), b.cuda(), r.cuda())
+    torch.cuda.synchronize()
+    want = of.gemm_bias(a, w, b) + r.float()
+    assert got.shape == (4, 96, 256) and _err(got, want) <= 2e-3 * max(1.0, want.abs().max().item())
+
+
+@pytest.mark.parametrize("hidden", [64, 256, 768, 1024, 1536, 4096])
+def test_layernorm_with_bias_and_residual(hidden):
+    import stof_b200
+    x, bias, res = _rand((37, hidden), 11), _rand((hidden,), 12), _rand((37, hidden), 13)
+    gamma, beta = _rand((hidden,), 14, 0.3) + 1, _rand((hidden,), 15, 0.3)
+    for eps in (1e-5, 1e-12):
+        got = stof_b200.bias_residual_layernorm(x.cuda(), bias.cuda(), res.cuda(), gamma.cuda(), beta.cuda(), eps)
+        torch.cuda.synchronize()
+        want = torch.nn.functional.layer_norm(x.float() + bias.float() + res.float(), (hidden,), gamma.float(), beta.float(), eps)
+        assert _err(got, want) <= 2e-3 * max(1.0, want.abs().max().item())
+    got = stof_b200.bias_residual_layernorm(x.cuda())
+    want = torch.nn.functional.layer_norm(x.float(), (hidden,), None, None, 1e-5)
+    assert _err(got, want) <= 3e-3
+
+
+def test_reference_fused_operator_signatures():
+    from triton_template.add_layernorm import triton_batched_bias_layernorm
+    from triton_template.gemm_add_layernorm import triton_matmul_bias_layernorm
+    from triton_template.gemm_gemm import triton_matmul_batch
+    B, M, K, N = 2, 128, 256, 512
+    A, W, bias = _rand((B, M, K), 20), _rand((K, N), 21, 0.1), _rand((N,), 22)
+    got = triton_matmul_bias_layernorm(A.cuda(), W.cuda().unsqueeze(0).expand(B, -1, -1), bias.cuda())
+    want = of.matmul_bias_layernorm(A, W.unsqueeze(0).expand(B, -1, -1), bias)
+    assert _err(got, want) <= 4e-3
+    Wb = _rand((B, K, N), 23, 0.1)
+    got = triton_matmul_bias_layernorm(A.cuda(), Wb.cuda(), bias.cuda(), 1e-6)
+    assert _err(got, of.matmul_bias_layernorm(A, Wb, bias, 1e-6)) <= 4e-3
+    d = _rand((N, K), 24, 0.05)
+    got = triton_matmul_batch(A.cuda(), W.cuda(), d.cuda(), bias.cuda())
+    want = of.matmul_gelu_matmul(A, W, d, bias)
+    assert _err(got, want) <= 2e-3 * max(1.0, want.abs().max().item())
+    x, w, b = _rand((B, M, N), 25), _rand((N,), 26), _rand((N,), 27)
+    got = triton_batched_bias_layernorm(x.cuda(), bias.cuda(), w.cuda(), b.cuda())
+    assert _err(got, of.bias_layernorm(x, bias, w, b)) <= 4e-3
+
+
+def test_encoder_layer_against_reference_function_fixture():
+    """One BERT layer on the inputs of the fixture produced by the reference's bert_fwd_std (eps 1e-5, causal mask)."""
+    import stof_b200
+    z = np.load(os.path.join(GOLDEN, "bert_layer.npz"))
+    params = {k[2:]: torch.from_numpy(z[k]) for k in z.files if k.startswith("p_")}
+    hidden = torch.from_numpy(z["hidden16"])
+    B, S, hid = hidden.shape
+    enc = stof_b200.BertEncoder([stof_b200.EncoderWeights.from_dict(params, "cuda")], head_num=2, eps=1e-5, block_m=32, block_n=32)
+    enc.set_mask(torch.tril(torch.ones(1, S, S)).cuda())
+    got = enc(hidden.cuda())
+    torch.cuda.synchronize()
+    # post-LN outputs are O(1..4); tolerance = the task's 2e-3 scaled by the output magnitude (fp16 ulp grows with it)
+    want = torch.from_numpy(z["out_f32"])
+    assert _err(got, want) <= 2e-3 * max(1.0, want.abs().max().item())
+
+
+def test_encoder_config4_shape_one_layer_slice():
+    """BERT-base layer (hidden 768, 12 heads, FFN 3072, eps 1e-12, sliding +-2 blocks) on 2 sequences of 1024."""
+    import stof_b200
+    B, S, hid, heads, ffn = 2, 1024, 768, 12, 3072
+    params = of.make_bert_params(hid, ffn, 1, seed=3)
+    g = torch.Generator().manual_seed(3)
+    hidden = torch.randn(B, S, hid, generator=g).half()
+    mask = om.recipe_mask("cfg4_sliding2_S1024")
+    enc = stof_b200.BertEncoder([stof_b200.EncoderWeights.from_dict(params[0], "cuda")], head_num=heads, eps=1e-12)
+    enc.set_mask(torch.from_numpy(mask).cuda())
+    got = enc(hidden.cuda())
+    torch.cuda.synchronize()
+    want = of.bert_layer(hidden, params[0], torch.from_numpy(mask.astype(np.float32)), heads, eps=1e-12)
+    assert _err(got, want) <= 2e-3 * max(1.0, want.abs().max().item())
