@@ -153,6 +153,8 @@ def run_attention(args, rank, world, local):
     from stof_b200 import _lib, dist as sd, workloads as wl
     dev = torch.device("cuda", local)
     cfg = wl.ATTENTION_CONFIGS[args.config]
+    if args.batch:
+        cfg = wl.AttentionConfig(cfg.name + f"_batch{args.batch}", args.batch, cfg.heads, cfg.seq_len, cfg.seed, cfg.mask)
     peaks = measured_peaks()
 
     # weak scaling: every rank runs the whole configuration on its own draw (seed + rank)
@@ -217,6 +219,11 @@ def run_attention(args, rank, world, local):
     total_flops = flops * world
     value = total_flops / (ms_per_step * 1e-3) / 1e12
 
+    if args.kernel_only:
+        if rank == 0:
+            print(json.dumps({"metric": "masked-MHA effective TFLOP/s", "value": value, "unit": "TFLOP/s", "ms_per_step": ms_per_step,
+                              "config": {"workload": cfg.name, "load_blocks": n_load}, "note": "kernel-only run (profiling aid)"}))
+        return 0
     # end to end through the reference-facing operator with host buffers: H2D of q,k,v, op (in place on q), D2H of the result
     from ops.package_op import block_attn_mask_op
     e2e_steps = args.steps
@@ -346,6 +353,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="stof", choices=["stof", "reference"])
     ap.add_argument("--workload", default="attention", choices=["attention", "encoder"])
+    ap.add_argument("--batch", type=int, default=0, help="override the batch size (profiling aid: smaller captures)")
+    ap.add_argument("--kernel-only", action="store_true", help="skip the end-to-end and CPU-baseline legs (profiling aid)")
     ap.add_argument("--config", default=None, help="cfg2 (default) or cfg3 for attention; cfg5 (default) or cfg4 for the encoder")
     args = ap.parse_args()
     if args.config is None:

@@ -23,7 +23,6 @@ constexpr int A_STAGES = 5;
 constexpr int A_Q_BYTES = A_TQ * A_D * 2;         // 16 KB
 constexpr int A_KV_BYTES = A_TKV * A_D * 2;       // 8 KB each for K and V
 constexpr int A_STAGE_BYTES = 2 * A_KV_BYTES;
-constexpr int A_P_BYTES = A_TQ * A_TKV * 2;       // 16 KB (only when P goes through shared memory)
 constexpr int A_THREADS = 192;
 constexpr int A_TMEM_COLS = 256;
 constexpr int A_COL_S = 0, A_COL_O = 128, A_COL_P = 192;   // S0 @0, S1 @64, O @128, P0 @192, P1 @224
@@ -58,16 +57,14 @@ __device__ __forceinline__ void tma_tile(void* dst, const CUtensorMap* map, uint
     tma_load_4d(dst, map, bar, c[0], c[1], c[2], c[3]);
 }
 
-template <bool P_IN_SMEM>
-__global__ void __launch_bounds__(A_THREADS, P_IN_SMEM ? 1 : 2)
+__global__ void __launch_bounds__(A_THREADS, 2)
 block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                   const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     unsigned char* q_smem = smem;
     unsigned char* kv_smem = q_smem + A_Q_BYTES;
-    unsigned char* p_smem = kv_smem + A_STAGES * A_STAGE_BYTES;
-    unsigned char* tail = p_smem + (P_IN_SMEM ? 2 * A_P_BYTES : 0);
+    unsigned char* tail = kv_smem + A_STAGES * A_STAGE_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(tail);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + AB_COUNT);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -196,12 +193,7 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     for (int kk = 0; kk < A_TKV / 16; ++kk) {
                         const uint64_t v_desc = make_smem_desc_sw128(v_addr + kk * 2048, 16, 1024);
                         const uint32_t acc = (j > 0 || kk > 0) ? 1u : 0u;
-                        if (P_IN_SMEM) {
-                            const uint32_t p_addr = smem_u32(p_smem + b * A_P_BYTES);
-                            mma_f16_ss(d, make_smem_desc_sw128(p_addr + kk * 32, 16, 1024), v_desc, idesc_pv, acc);
-                        } else {
-                            mma_f16_ts(d, tmem_base + A_COL_P + b * (A_TKV / 2) + kk * 8, v_desc, idesc_pv, acc);
-                        }
+                        mma_f16_ts(d, tmem_base + A_COL_P + b * (A_TKV / 2) + kk * 8, v_desc, idesc_pv, acc);
                     }
                     tc_commit(&bars[AB_KV_EMPTY + s]);
                     tc_commit(&bars[AB_PV_DONE + b]);
@@ -318,18 +310,9 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 }
                 // P buffer b is free once the PV product of tile j-2 has completed
                 if (j >= 2) mbar_wait(&bars[AB_PV_DONE + b], ((j - 2) >> 1) & 1, wctx, AB_PV_DONE + b);
-                if (P_IN_SMEM) {
-                    unsigned char* prow = p_smem + b * A_P_BYTES + lr * 128;
-#pragma unroll
-                    for (int c = 0; c < 8; ++c)
-                        *reinterpret_cast<uint4*>(prow + ((c ^ (lr & 7)) << 4)) =
-                            make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
-                    fence_proxy_async_smem();
-                } else {
-                    tc_fence_after();
-                    tmem_st32(t_lane + A_COL_P + b * (A_TKV / 2), packed);
-                    tc_wait_st();
-                }
+                tc_fence_after();
+                tmem_st32(t_lane + A_COL_P + b * (A_TKV / 2), packed);
+                tc_wait_st();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bars[AB_P_FULL + b]);
@@ -374,10 +357,10 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     }
 }
 
-size_t attn_smem_bytes(bool p_in_smem, int seq_len, int bm, int bn) {
+size_t attn_smem_bytes(int seq_len, int bm, int bn) {
     const int n_kv_tiles_all = (seq_len + A_TKV - 1) / A_TKV;
     const size_t table = static_cast<size_t>(A_TQ / bm) * (seq_len / bn) * 2;
-    return 1024 + A_Q_BYTES + static_cast<size_t>(A_STAGES) * A_STAGE_BYTES + (p_in_smem ? 2 * A_P_BYTES : 0) + AB_COUNT * 8 + 16 +
+    return 1024 + A_Q_BYTES + static_cast<size_t>(A_STAGES) * A_STAGE_BYTES + AB_COUNT * 8 + 16 +
            static_cast<size_t>((n_kv_tiles_all + 7) & ~7) * 2 + table + 16;
 }
 
@@ -402,17 +385,10 @@ int make_qkv_map(CUtensorMap* map, const void* base, int batch, int heads, int s
     return make_tensor_map_f16(map, base, 4, dims, strides, box);
 }
 
-int g_attn_variant = 0;   // 0: P through tensor memory, 1: P through shared memory
-
 }  // namespace
 }  // namespace stof
 
 using namespace stof;
-
-extern "C" int stof_debug_set_attn_variant(int v) {
-    g_attn_variant = v ? 1 : 0;
-    return STOF_OK;
-}
 
 extern "C" int stof_block_attn(const void* q, const void* k, const void* v, void* out, int batch, int heads, int seq_len, int head_dim,
                                const long long q_strides[3], const long long k_strides[3], const long long v_strides[3],
@@ -438,7 +414,6 @@ extern "C" int stof_block_attn(const void* q, const void* k, const void* v, void
         for (int i = 0; i < 3; ++i)
             STOF_REQUIRE(all[t][i] > 0 && all[t][i] % 8 == 0, "block_attn: strides must be positive multiples of 8 elements");
     }
-    const bool p_in_smem = g_attn_variant == 1;
     const size_t table_bytes = static_cast<size_t>(A_TQ / block_m) * (seq_len / block_n) * 2;
     if (table_bytes > A_MAX_TABLE_BYTES) {
         set_error("block_attn: seq_len %d with %dx%d blocks needs a %zu-byte block table, beyond the maximum of %d", seq_len, block_m, block_n,
@@ -459,15 +434,16 @@ extern "C" int stof_block_attn(const void* q, const void* k, const void* v, void
     if (int rc = make_qkv_map(&mk, k, batch, heads, seq_len, k_strides, A_TKV, &p.slot_s[1], &p.slot_h[1], &p.slot_b[1])) return rc;
     if (int rc = make_qkv_map(&mv, v, batch, heads, seq_len, v_strides, A_TKV, &p.slot_s[2], &p.slot_h[2], &p.slot_b[2])) return rc;
 
-    const size_t smem = attn_smem_bytes(p_in_smem, seq_len, block_m, block_n);
+    const size_t smem = attn_smem_bytes(seq_len, block_m, block_n);
     const dim3 grid((seq_len + A_TQ - 1) / A_TQ, heads, batch);
-    if (p_in_smem) {
-        STOF_CUDA(cudaFuncSetAttribute(block_attn_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-        block_attn_kernel<true><<<grid, A_THREADS, smem, stream>>>(mq, mk, mv, p);
-    } else {
-        STOF_CUDA(cudaFuncSetAttribute(block_attn_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-        block_attn_kernel<false><<<grid, A_THREADS, smem, stream>>>(mq, mk, mv, p);
+    static size_t configured_smem[64] = {};
+    int dev = 0;
+    STOF_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || configured_smem[dev] < smem) {
+        STOF_CUDA(cudaFuncSetAttribute(block_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        if (dev >= 0 && dev < 64) configured_smem[dev] = smem;
     }
+    block_attn_kernel<<<grid, A_THREADS, smem, stream>>>(mq, mk, mv, p);
     STOF_CUDA(cudaGetLastError());
     return STOF_OK;
 }
