@@ -206,7 +206,7 @@ def run_attention(args, rank, world, local):
         torch.cuda.synchronize(dev)
         wall = time.perf_counter() - t_wall
         # keep the GPU under the same load a little longer so that the clock sampler sees it
-        t_end = time.perf_counter() + 0.25
+        t_end = time.perf_counter() + (0.0 if args.kernel_only else 0.25)
         while time.perf_counter() < t_end:
             step()
         torch.cuda.synchronize(dev)

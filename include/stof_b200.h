@@ -67,22 +67,32 @@ int stof_mask_fill(const void* mask, int mask_dtype, int seq_len, int block_m, i
  * Replaces: launch_block_attn_mask(...), src/ops/src/block_attn_mask_cuda.cu:6026-6316, as bound by
  *           block_attn_mask_gpu, src/ops/src/block_attn_mask.cpp:17-49.
  *
- * For each row block only the column blocks of the full_* and part_* lists take part; a partial
- * block adds its fp16 tile to the unscaled scores before the softmax scale, as the reference kernel
- * does.  A row without any listed key yields zeros.  `out` may alias `q` (the reference overwrites
- * q): every thread block reads its own query rows before it writes them.
+ * Two calls.  stof_block_attn_plan turns the block index (the full_* and part_* lists of
+ * get_sparse_storage) into the kernel's own 128 x 64 tiling: per 128-row query tile the ordered list
+ * of 64-wide key tiles that any of its row blocks lists, a code per 16 x 16 group (absent / full /
+ * partial tile i) and the order in which the scheduler visits the query tiles.  It depends on the
+ * index only, so one plan serves every call with that index (every layer of an encoder).  The plan
+ * buffer is caller-owned scratch of stof_block_attn_plan_bytes() bytes.
+ * stof_block_attn runs the attention.  For each row block only the listed column blocks take part; a
+ * partial block adds its fp16 tile to the unscaled scores before the softmax scale, as the reference
+ * kernel does.  A row without any listed key yields zeros.  `out` may alias `q` (the reference
+ * overwrites q): a query tile is read completely before its rows are written.
  * Strides are in elements for (batch, head, row); the innermost (head_dim) stride is 1.  All base
- * pointers 16-byte aligned, strides multiples of 8 elements.  block_m in {16,32,64,128}, block_n in
- * {16,32,64,128}; seq_len a multiple of both.  `num_warps` is accepted for signature compatibility
- * and ignored.  load_row_ptr / load_col_idx may be NULL (they are the merge of the other two lists).
+ * pointers 16-byte aligned, strides multiples of 8 elements.  block_m, block_n in {16,32,64,128};
+ * seq_len a multiple of both.  `num_warps` is accepted for signature compatibility and ignored.
  * ------------------------------------------------------------------------------------------ */
+size_t stof_block_attn_plan_bytes(int seq_len, int block_m, int block_n);
+
+int stof_block_attn_plan(const int* full_row_ptr, const int* full_col_idx,
+                         const int* part_row_ptr, const int* part_col_idx,
+                         int seq_len, int block_m, int block_n,
+                         void* plan, size_t plan_bytes, int* status_dev, void* stream);
+
 int stof_block_attn(const void* q, const void* k, const void* v, void* out,
                     int batch, int heads, int seq_len, int head_dim,
                     const long long q_strides[3], const long long k_strides[3],
                     const long long v_strides[3], const long long out_strides[3],
-                    const int* full_row_ptr, const int* full_col_idx,
-                    const int* part_row_ptr, const int* part_col_idx, const void* part_block_mask,
-                    const int* load_row_ptr, const int* load_col_idx,
+                    const int* part_row_ptr, const void* part_block_mask, const void* plan,
                     int block_m, int block_n, int num_warps, float softmax_scale,
                     int* status_dev, void* stream);
 

@@ -1,17 +1,23 @@
 // Block-masked multi-head attention for sm_100a: TMA-fed tcgen05 MMAs with the accumulators in tensor
 // memory, online softmax in registers, only listed K/V blocks ever loaded.
 //
-// One thread block owns 128 query rows of one (batch, head) and walks the union of the 64-wide K/V
-// tiles that any of its row blocks lists (block sizes 16..128 are mapped onto this 128 x 64 tiling
-// through a small per-block code table in shared memory: 0 absent, 1 full, 2+i partial tile i).
-//   warp 4      TMA producer: Q tile once, then (K, V) tile pairs through a ring of stages
+// Tiling.  A work item is 128 query rows of one (batch, head); it walks the union of the 64-wide K/V
+// tiles that any of its row blocks lists.  Block sizes 16..128 are mapped onto this 128 x 64 tiling by a
+// PLAN built once per block index (plan_kernel): per query tile the ordered tile list and, per tile, one
+// code for each 16-row x 16-column group (0 absent, 1 full, 2+i partial tile i of the row block).
+//
+// Kernel.  Persistent, two thread blocks per SM, static schedule over the items (heavy query tiles first
+// inside groups of (batch, head) pairs small enough to keep their K/V in L2):
+//   warp 4      TMA producer: Q tiles (double buffered) and (K, V) tile pairs through a ring of stages
 //   warp 5      MMA issuer:   S = Q K^T (128 x 64 x 64) into one of two S buffers in tensor memory, and
-//               O += P V (128 x 64 x 64) with P read from tensor memory (fp16) and V consumed in its natural
-//               (key-row major) layout through an MN-major descriptor
-//   warps 0-3   softmax: one query row per thread (tensor-memory lane), scores via tcgen05.ld, masking per
-//               row block, exp2 with the scale folded in, running max with lazy rescale of O (only when
-//               the maximum grew by more than 2^8), P written back with tcgen05.st
-// Row blocks that do not list a tile skip its exponentials (P = 0); tiles nobody lists are never loaded.
+//               O += P V with P read back from tensor memory (fp16, stored over the S buffer it came from)
+//               and V consumed in its natural key-row-major layout through an MN-major descriptor;
+//               O is double buffered across items so that an item's epilogue overlaps the next item
+//   warps 0-3   softmax: one query row per thread (tensor-memory lane): tcgen05.ld of the scores, masking
+//               from the plan codes, exp2 with the scale folded into one FMA, running maximum with a lazy
+//               rescale of O (only when the maximum grew by more than 2^8), P written with tcgen05.st,
+//               final O / l normalisation and 128-bit stores
+// Row groups that do not list a tile skip its exponentials (P = 0); tiles nobody lists are never loaded.
 #include "stof_host.h"
 #include "stof_ptx.cuh"
 
@@ -19,78 +25,230 @@ namespace stof {
 namespace {
 
 constexpr int A_TQ = 128, A_TKV = 64, A_D = 64;
-constexpr int A_STAGES = 5;
-constexpr int A_Q_BYTES = A_TQ * A_D * 2;         // 16 KB
+constexpr int A_STAGES = 4;
+constexpr int A_Q_BYTES = A_TQ * A_D * 2;         // 16 KB per Q buffer
 constexpr int A_KV_BYTES = A_TKV * A_D * 2;       // 8 KB each for K and V
 constexpr int A_STAGE_BYTES = 2 * A_KV_BYTES;
 constexpr int A_THREADS = 192;
+constexpr int A_CTAS_PER_SM = 2;
 constexpr int A_TMEM_COLS = 256;
-constexpr int A_COL_S = 0, A_COL_O = 128, A_COL_P = 192;   // S0 @0, S1 @64, O @128, P0 @192, P1 @224
-constexpr int A_MAX_TABLE_BYTES = 24 * 1024;
+constexpr int A_COL_S = 0, A_COL_O = 128;         // S0 @0, S1 @64 (P overlays the first 32 columns of its S), O0 @128, O1 @192
+constexpr int A_MAX_TABLE_BYTES = 48 * 1024;
 constexpr float A_RESCALE_THRESHOLD = 8.0f;       // log2 units
+constexpr int A_GROUP_BH = 40;                    // (batch, head) pairs per scheduling group: 40 x 2 x S x 128 B of K/V stay in L2
 
 enum {
-    AB_Q = 0, AB_KV_FULL = 1, AB_KV_EMPTY = AB_KV_FULL + A_STAGES, AB_S_FULL = AB_KV_EMPTY + A_STAGES, AB_P_FULL = AB_S_FULL + 2,
-    AB_PV_DONE = AB_P_FULL + 2, AB_COUNT = AB_PV_DONE + 2
+    AB_Q_FULL = 0, AB_Q_EMPTY = 2, AB_KV_FULL = 4, AB_KV_EMPTY = AB_KV_FULL + A_STAGES, AB_S_FULL = AB_KV_EMPTY + A_STAGES,
+    AB_P_FULL = AB_S_FULL + 2, AB_PV_DONE = AB_P_FULL + 2, AB_O_FREE = AB_PV_DONE + 2, AB_COUNT = AB_O_FREE + 2
 };
 
+// ---------------------------------------------------------------------------------------------
+// Plan layout (all offsets from the start of the plan buffer, 16-byte aligned sections)
+// ---------------------------------------------------------------------------------------------
+struct PlanHeader {
+    int magic, seq_len, bm, bn;
+    int n_qtiles, max_tiles, total_steps, reserved;
+};
+constexpr int PLAN_MAGIC = 0x53544F46;
+__host__ __device__ inline size_t plan_off_ntiles() { return sizeof(PlanHeader); }
+__host__ __device__ inline size_t plan_off_order(int nqt) { return plan_off_ntiles() + ((static_cast<size_t>(nqt) * 4 + 15) & ~static_cast<size_t>(15)); }
+__host__ __device__ inline size_t plan_off_tiles(int nqt) { return plan_off_order(nqt) + ((static_cast<size_t>(nqt) * 8 + 15) & ~static_cast<size_t>(15)); }
+__host__ __device__ inline size_t plan_off_codes(int nqt, int maxt) {
+    return plan_off_tiles(nqt) + ((static_cast<size_t>(nqt) * maxt * 2 + 15) & ~static_cast<size_t>(15));
+}
+__host__ __device__ inline size_t plan_total_bytes(int nqt, int maxt) { return plan_off_codes(nqt, maxt) + static_cast<size_t>(nqt) * maxt * 64; }
+
+// One thread block per query tile: code table in shared memory -> ordered tile list + 8x4 group codes per tile.
+// The last block to finish ranks the query tiles by tile count (descending, stable) for the scheduler.
+__global__ void __launch_bounds__(256)
+plan_kernel(const int* __restrict__ full_row_ptr, const int* __restrict__ full_col_idx, const int* __restrict__ part_row_ptr,
+            const int* __restrict__ part_col_idx, int seq_len, int bm, int bn, unsigned char* plan, unsigned int* ticket, int* status) {
+    extern __shared__ uint16_t table[];                 // [nrb][ncb]
+    __shared__ int s_count;
+    __shared__ bool s_last;
+    const int nqt = gridDim.x, maxt = (seq_len + A_TKV - 1) / A_TKV;
+    const int qt = blockIdx.x;
+    const int nbm = seq_len / bm, ncb = seq_len / bn, nrb = A_TQ / bm;
+    int* n_tiles = reinterpret_cast<int*>(plan + plan_off_ntiles());
+    int2* order = reinterpret_cast<int2*>(plan + plan_off_order(nqt));     // per rank: {query tile, tile count}
+    uint16_t* tiles = reinterpret_cast<uint16_t*>(plan + plan_off_tiles(nqt)) + static_cast<size_t>(qt) * maxt;
+    uint16_t* codes = reinterpret_cast<uint16_t*>(plan + plan_off_codes(nqt, maxt)) + static_cast<size_t>(qt) * maxt * 32;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+    for (int i = threadIdx.x; i < nrb * ncb; i += blockDim.x) table[i] = 0;
+    __syncthreads();
+    for (int lrb = 0; lrb < nrb; ++lrb) {
+        const int rb = qt * nrb + lrb;
+        if (rb >= nbm) break;
+        const int f0 = full_row_ptr[rb], f1 = full_row_ptr[rb + 1];
+        for (int i = f0 + threadIdx.x; i < f1; i += blockDim.x) {
+            const int c = full_col_idx[i];
+            if (c >= 0 && c < ncb) table[lrb * ncb + c] = 1;
+            else if (status) atomicCAS(status, 0, STATUS_BAD_INDEX);
+        }
+        const int p0 = part_row_ptr[rb], p1 = part_row_ptr[rb + 1];
+        for (int i = p0 + threadIdx.x; i < p1; i += blockDim.x) {
+            const int c = part_col_idx[i];
+            if (c >= 0 && c < ncb && i - p0 < 65534) table[lrb * ncb + c] = static_cast<uint16_t>(2 + (i - p0));
+            else if (status) atomicCAS(status, 0, STATUS_BAD_INDEX);
+        }
+    }
+    __syncthreads();
+    if (warp == 0) {
+        int count = 0;
+        for (int t0 = 0; t0 < maxt; t0 += 32) {
+            const int t = t0 + lane;
+            bool active = false;
+            if (t < maxt) {
+                const int c_lo = (t * A_TKV) / bn;
+                const int c_hi = min(ncb - 1, (t * A_TKV + A_TKV - 1) / bn);
+                for (int lrb = 0; lrb < nrb; ++lrb)
+                    for (int c = c_lo; c <= c_hi; ++c) active |= table[lrb * ncb + c] != 0;
+            }
+            const unsigned bal = __ballot_sync(0xffffffffu, active);
+            if (active) tiles[count + __popc(bal & ((1u << lane) - 1u))] = static_cast<uint16_t>(t);
+            count += __popc(bal);
+        }
+        if (lane == 0) {
+            s_count = count;
+            n_tiles[qt] = count;
+        }
+    }
+    __syncthreads();
+    const int count = s_count;
+    // codes[j][row group 0..7][col group 0..3]
+    for (int i = threadIdx.x; i < count * 32; i += blockDim.x) {
+        const int j = i >> 5, rg = (i >> 2) & 7, cg = i & 3;
+        const int t = tiles[j];
+        const int row = qt * A_TQ + rg * 16, col = t * A_TKV + cg * 16;
+        uint16_t code = 0;
+        if (row < seq_len && col < seq_len) code = table[((rg * 16) / bm) * ncb + col / bn];
+        codes[i] = code;
+    }
+    // the last block orders the query tiles by descending tile count (stable)
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned t = atomicAdd(ticket, 1u);
+        s_last = (t == gridDim.x - 1);
+        if (s_last) *ticket = 0;
+    }
+    __syncthreads();
+    if (s_last) {
+        __threadfence();
+        PlanHeader* h = reinterpret_cast<PlanHeader*>(plan);
+        int total = 0;
+        for (int a = threadIdx.x; a < nqt; a += blockDim.x) {
+            const int na = __ldcg(n_tiles + a);
+            int rank = 0;
+            for (int b = 0; b < nqt; ++b) {
+                const int nb2 = __ldcg(n_tiles + b);
+                rank += (nb2 > na || (nb2 == na && b < a)) ? 1 : 0;
+            }
+            order[rank] = make_int2(a, na);
+            total += na;
+        }
+        atomicAdd(&h->total_steps, total);
+        if (threadIdx.x == 0) {
+            h->magic = PLAN_MAGIC; h->seq_len = seq_len; h->bm = bm; h->bn = bn;
+            h->n_qtiles = nqt; h->max_tiles = maxt; h->reserved = 0;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Attention kernel
+// ---------------------------------------------------------------------------------------------
 struct AttnParams {
     __half* out;
     long long o_stride_b, o_stride_h, o_stride_s;
-    const int* full_row_ptr;
-    const int* full_col_idx;
     const int* part_row_ptr;
-    const int* part_col_idx;
     const __half* part_block_mask;
+    const unsigned char* plan;
     int batch, heads, seq_len;
-    int bm, bn;
+    int bm, bn, bm_shift, bn_shift;
+    int n_qtiles, max_tiles;
+    unsigned total_items, bh_total;
     int slot_s[3], slot_h[3], slot_b[3];   // coordinate slot (1..3) of row / head / batch in the q, k, v tensor maps
     float scale_log2;
     int* status;
+#ifdef STOF_TRACE
+    long long* trace;
+#endif
 };
 
 __device__ __forceinline__ void tma_tile(void* dst, const CUtensorMap* map, uint64_t* bar, int row, int h, int b, int ss, int sh, int sb) {
-    int c[4] = {0, 0, 0, 0};
-    c[ss] = row;
-    c[sh] = h;
-    c[sb] = b;
-    tma_load_4d(dst, map, bar, c[0], c[1], c[2], c[3]);
+    const int c1 = ss == 1 ? row : (sh == 1 ? h : b);
+    const int c2 = ss == 2 ? row : (sh == 2 ? h : b);
+    const int c3 = ss == 3 ? row : (sh == 3 ? h : b);
+    tma_load_4d(dst, map, bar, 0, c1, c2, c3);
 }
 
-__global__ void __launch_bounds__(A_THREADS, 2)
+// Static schedule: items are enumerated group by group ((batch, head) pairs in chunks of A_GROUP_BH), inside a
+// group query-tile-rank major (heaviest tiles first), and dealt round-robin to the thread blocks.
+struct Item {
+    int qt, head, batch, n;
+    bool valid;
+};
+__device__ __forceinline__ Item fetch_item(unsigned k, const AttnParams& p, const int2* sched) {
+    Item it;
+    it.qt = 0; it.head = 0; it.batch = 0; it.n = 0;
+    const unsigned idx = blockIdx.x + k * gridDim.x;
+    it.valid = idx < p.total_items;
+    if (!it.valid) return it;
+    const unsigned group_items = static_cast<unsigned>(A_GROUP_BH) * p.n_qtiles;
+    const unsigned g = idx / group_items;
+    const unsigned r = idx - g * group_items;
+    const unsigned bh0 = g * A_GROUP_BH;
+    const unsigned gsize = min(static_cast<unsigned>(A_GROUP_BH), p.bh_total - bh0);     // the tail group is smaller
+    const unsigned rank = r / gsize;
+    const unsigned bh = bh0 + (r - rank * gsize);
+    const int2 sc = __ldg(sched + rank);
+    it.qt = sc.x;
+    it.n = sc.y;
+    it.batch = static_cast<int>(bh / p.heads);
+    it.head = static_cast<int>(bh - it.batch * p.heads);
+    return it;
+}
+
+#ifdef STOF_TRACE
+#define TRACE(slot, step) do { if (blockIdx.x == 0 && (step) < 256) p.trace[(step) * 8 + (slot)] = clock64(); } while (0)
+#else
+#define TRACE(slot, step) do { } while (0)
+#endif
+
+__device__ __forceinline__ float max3(float a, float b, float c) { return fmaxf(a, fmaxf(b, c)); }
+
+__global__ void __launch_bounds__(A_THREADS, A_CTAS_PER_SM)
 block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                   const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    unsigned char* q_smem = smem;
-    unsigned char* kv_smem = q_smem + A_Q_BYTES;
-    unsigned char* tail = kv_smem + A_STAGES * A_STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(tail);
+    unsigned char* q_smem = smem;                                   // 2 buffers
+    unsigned char* kv_smem = q_smem + 2 * A_Q_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(kv_smem + A_STAGES * A_STAGE_BYTES);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + AB_COUNT);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    int* n_tiles_smem = reinterpret_cast<int*>(tmem_slot + 2);
-    uint16_t* tile_list = reinterpret_cast<uint16_t*>(tmem_slot + 4);
-    const int n_kv_tiles_all = (p.seq_len + A_TKV - 1) / A_TKV;
-    uint16_t* table = tile_list + ((n_kv_tiles_all + 7) & ~7);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int qt = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
-    const int nbm = p.seq_len / p.bm, ncb = p.seq_len / p.bn;
-    const int nrb = A_TQ / p.bm;                       // row blocks per thread block (1..8)
     const WaitCtx wctx{abort_flag, p.status};
+    const int2* plan_sched = reinterpret_cast<const int2*>(p.plan + plan_off_order(p.n_qtiles));
+    const uint16_t* plan_tiles = reinterpret_cast<const uint16_t*>(p.plan + plan_off_tiles(p.n_qtiles));
+    const uint16_t* plan_codes = reinterpret_cast<const uint16_t*>(p.plan + plan_off_codes(p.n_qtiles, p.max_tiles));
 
-    // ------------------------------------------------------------------ prologue
     if (threadIdx.x == 0) {
         *abort_flag = (p.status != nullptr && *p.status != 0) ? 1 : 0;
-        mbar_init(&bars[AB_Q], 1);
-        for (int i = 0; i < A_STAGES; ++i) {
-            mbar_init(&bars[AB_KV_FULL + i], 1);
-            mbar_init(&bars[AB_KV_EMPTY + i], 1);
-        }
         for (int i = 0; i < 2; ++i) {
+            mbar_init(&bars[AB_Q_FULL + i], 1);
+            mbar_init(&bars[AB_Q_EMPTY + i], 1);
             mbar_init(&bars[AB_S_FULL + i], 1);
             mbar_init(&bars[AB_P_FULL + i], 4);
             mbar_init(&bars[AB_PV_DONE + i], 1);
+            mbar_init(&bars[AB_O_FREE + i], 4);
+        }
+        for (int i = 0; i < A_STAGES; ++i) {
+            mbar_init(&bars[AB_KV_FULL + i], 1);
+            mbar_init(&bars[AB_KV_EMPTY + i], 1);
         }
         fence_mbar_init();
     }
@@ -98,68 +256,45 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         tmem_alloc(tmem_slot, A_TMEM_COLS);
         tmem_relinquish();
     }
-    for (int i = threadIdx.x; i < nrb * ncb; i += blockDim.x) table[i] = 0;
-    __syncthreads();
-    for (int lrb = 0; lrb < nrb; ++lrb) {
-        const int rb = qt * nrb + lrb;
-        if (rb >= nbm) break;
-        const int f0 = p.full_row_ptr[rb], f1 = p.full_row_ptr[rb + 1];
-        for (int i = f0 + threadIdx.x; i < f1; i += blockDim.x) {
-            const int c = p.full_col_idx[i];
-            if (c >= 0 && c < ncb) table[lrb * ncb + c] = 1;
-            else if (p.status) atomicCAS(p.status, 0, STATUS_BAD_INDEX);
-        }
-        const int p0 = p.part_row_ptr[rb], p1 = p.part_row_ptr[rb + 1];
-        for (int i = p0 + threadIdx.x; i < p1; i += blockDim.x) {
-            const int c = p.part_col_idx[i];
-            if (c >= 0 && c < ncb) table[lrb * ncb + c] = static_cast<uint16_t>(2 + (i - p0));
-            else if (p.status) atomicCAS(p.status, 0, STATUS_BAD_INDEX);
-        }
-    }
-    __syncthreads();
-    if (warp == 0) {
-        // ordered list of the 64-wide K/V tiles that at least one row block of this thread block lists
-        int count = 0;
-        for (int t0 = 0; t0 < n_kv_tiles_all; t0 += 32) {
-            const int t = t0 + lane;
-            bool active = false;
-            if (t < n_kv_tiles_all) {
-                const int c_lo = (t * A_TKV) / p.bn;
-                const int c_hi = min(ncb - 1, (t * A_TKV + A_TKV - 1) / p.bn);
-                for (int lrb = 0; lrb < nrb; ++lrb)
-                    for (int c = c_lo; c <= c_hi; ++c) active |= table[lrb * ncb + c] != 0;
-            }
-            const unsigned bal = __ballot_sync(0xffffffffu, active);
-            if (active) tile_list[count + __popc(bal & ((1u << lane) - 1u))] = static_cast<uint16_t>(t);
-            count += __popc(bal);
-        }
-        if (lane == 0) *n_tiles_smem = count;
-    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const int n_tiles = *n_tiles_smem;
-    const int q_row0 = qt * A_TQ;
 
-    if (*abort_flag == 0 && n_tiles > 0) {
+    if (*abort_flag == 0) {
         if (warp == 4) {
             // -------------------------------------------------------------- TMA producer
             if (elect_one()) {
                 tma_prefetch_desc(&map_q);
                 tma_prefetch_desc(&map_k);
                 tma_prefetch_desc(&map_v);
-                mbar_arrive_expect_tx(&bars[AB_Q], A_Q_BYTES);
-                tma_tile(q_smem, &map_q, &bars[AB_Q], q_row0, head, batch, p.slot_s[0], p.slot_h[0], p.slot_b[0]);
-                for (int j = 0; j < n_tiles; ++j) {
-                    const int s = j % A_STAGES;
-                    const uint32_t ph = (j / A_STAGES) & 1;
-                    mbar_wait(&bars[AB_KV_EMPTY + s], ph ^ 1, wctx, AB_KV_EMPTY + s);
-                    const int kv_row = static_cast<int>(tile_list[j]) * A_TKV;
-                    unsigned char* k_dst = kv_smem + s * A_STAGE_BYTES;
-                    mbar_arrive_expect_tx(&bars[AB_KV_FULL + s], A_STAGE_BYTES);
-                    tma_tile(k_dst, &map_k, &bars[AB_KV_FULL + s], kv_row, head, batch, p.slot_s[1], p.slot_h[1], p.slot_b[1]);
-                    tma_tile(k_dst + A_KV_BYTES, &map_v, &bars[AB_KV_FULL + s], kv_row, head, batch, p.slot_s[2], p.slot_h[2], p.slot_b[2]);
+                int it = 0;
+                long long g = 0;
+                Item item = fetch_item(0, p, plan_sched);
+                for (unsigned k = 0; item.valid; ++k) {
+                    const Item next = fetch_item(k + 1, p, plan_sched);      // its loads complete while this item streams
+                    const Item cur = item;
+                    item = next;
+                    const int n = cur.n;
+                    if (n == 0) continue;
+                    const int qb = it & 1;
+                    mbar_wait(&bars[AB_Q_EMPTY + qb], ((it >> 1) & 1) ^ 1, wctx, AB_Q_EMPTY + qb);
+                    mbar_arrive_expect_tx(&bars[AB_Q_FULL + qb], A_Q_BYTES);
+                    tma_tile(q_smem + qb * A_Q_BYTES, &map_q, &bars[AB_Q_FULL + qb], cur.qt * A_TQ, cur.head, cur.batch, p.slot_s[0],
+                             p.slot_h[0], p.slot_b[0]);
+                    const uint16_t* tl = plan_tiles + static_cast<size_t>(cur.qt) * p.max_tiles;
+                    for (int j = 0; j < n; ++j, ++g) {
+                        const int s = static_cast<int>(g % A_STAGES);
+                        const uint32_t ph = static_cast<uint32_t>((g / A_STAGES) & 1);
+                        mbar_wait(&bars[AB_KV_EMPTY + s], ph ^ 1, wctx, AB_KV_EMPTY + s);
+                        const int kv_row = static_cast<int>(tl[j]) * A_TKV;
+                        unsigned char* k_dst = kv_smem + s * A_STAGE_BYTES;
+                        mbar_arrive_expect_tx(&bars[AB_KV_FULL + s], A_STAGE_BYTES);
+                        tma_tile(k_dst, &map_k, &bars[AB_KV_FULL + s], kv_row, cur.head, cur.batch, p.slot_s[1], p.slot_h[1], p.slot_b[1]);
+                        tma_tile(k_dst + A_KV_BYTES, &map_v, &bars[AB_KV_FULL + s], kv_row, cur.head, cur.batch, p.slot_s[2], p.slot_h[2],
+                                 p.slot_b[2]);
+                    }
+                    ++it;
                 }
             }
         } else if (warp == 5) {
@@ -167,186 +302,266 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             if (elect_one()) {
                 constexpr uint32_t idesc_qk = make_idesc_f16(A_TQ, A_TKV, /*b_mn_major=*/false);
                 constexpr uint32_t idesc_pv = make_idesc_f16(A_TQ, A_D, /*b_mn_major=*/true);
-                const uint32_t q_addr = smem_u32(q_smem);
-                mbar_wait(&bars[AB_Q], 0, wctx, AB_Q);
-                auto issue_qk = [&](int j) {
-                    const int s = j % A_STAGES;
-                    mbar_wait(&bars[AB_KV_FULL + s], (j / A_STAGES) & 1, wctx, AB_KV_FULL + s);
+                // S = Q K^T of global step g, reading Q buffer qb
+                auto issue_qk = [&](long long g, int qb) {
+                    const int s = static_cast<int>(g % A_STAGES);
+                    mbar_wait(&bars[AB_KV_FULL + s], static_cast<uint32_t>((g / A_STAGES) & 1), wctx, AB_KV_FULL + s);
                     tc_fence_after();
+                    const uint32_t q_addr = smem_u32(q_smem + qb * A_Q_BYTES);
                     const uint32_t k_addr = smem_u32(kv_smem + s * A_STAGE_BYTES);
-                    const uint32_t d = tmem_base + A_COL_S + (j & 1) * A_TKV;
+                    const uint32_t d = tmem_base + A_COL_S + static_cast<uint32_t>(g & 1) * A_TKV;
 #pragma unroll
                     for (int kk = 0; kk < A_D / 16; ++kk)
                         mma_f16_ss(d, make_smem_desc_sw128(q_addr + kk * 32, 16, 1024), make_smem_desc_sw128(k_addr + kk * 32, 16, 1024),
                                    idesc_qk, kk > 0 ? 1u : 0u);
-                    tc_commit(&bars[AB_S_FULL + (j & 1)]);
+                    tc_commit(&bars[AB_S_FULL + (g & 1)]);
                 };
-                issue_qk(0);
-                for (int j = 0; j < n_tiles; ++j) {
-                    if (j + 1 < n_tiles) issue_qk(j + 1);
-                    const int b = j & 1, s = j % A_STAGES;
-                    mbar_wait(&bars[AB_P_FULL + b], (j >> 1) & 1, wctx, AB_P_FULL + b);
-                    tc_fence_after();
-                    const uint32_t v_addr = smem_u32(kv_smem + s * A_STAGE_BYTES + A_KV_BYTES);
-                    const uint32_t d = tmem_base + A_COL_O;
-#pragma unroll
-                    for (int kk = 0; kk < A_TKV / 16; ++kk) {
-                        const uint64_t v_desc = make_smem_desc_sw128(v_addr + kk * 2048, 16, 1024);
-                        const uint32_t acc = (j > 0 || kk > 0) ? 1u : 0u;
-                        mma_f16_ts(d, tmem_base + A_COL_P + b * (A_TKV / 2) + kk * 8, v_desc, idesc_pv, acc);
+                // next non-empty item of this thread block, starting at schedule position k
+                auto next_item = [&](unsigned& k, int& n) -> bool {
+                    for (;;) {
+                        const Item item = fetch_item(k, p, plan_sched);
+                        if (!item.valid) return false;
+                        ++k;
+                        n = item.n;
+                        if (n > 0) return true;
                     }
-                    tc_commit(&bars[AB_KV_EMPTY + s]);
-                    tc_commit(&bars[AB_PV_DONE + b]);
+                };
+                unsigned k = 0;
+                long long g = 0;
+                int it = 0, n = 0, n_next = 0;
+                bool have = next_item(k, n);
+                if (have) {
+                    mbar_wait(&bars[AB_Q_FULL + 0], 0, wctx, AB_Q_FULL);
+                    issue_qk(0, 0);
+                }
+                while (have) {
+                    const bool have_next = next_item(k, n_next);
+                    const int qb = it & 1;
+                    for (int j = 0; j < n; ++j, ++g) {
+                        if (j + 1 < n) {
+                            issue_qk(g + 1, qb);
+                        } else {
+                            tc_commit(&bars[AB_Q_EMPTY + qb]);                   // every QK^T of this item has been issued
+                            if (have_next) {
+                                const int qn = (it + 1) & 1;
+                                mbar_wait(&bars[AB_Q_FULL + qn], static_cast<uint32_t>(((it + 1) >> 1) & 1), wctx, AB_Q_FULL + qn);
+                                issue_qk(g + 1, qn);
+                            }
+                        }
+                        if (j == 0) {
+                            mbar_wait(&bars[AB_O_FREE + qb], static_cast<uint32_t>(((it >> 1) & 1) ^ 1), wctx, AB_O_FREE + qb);
+                        }
+                        const int b = static_cast<int>(g & 1), s = static_cast<int>(g % A_STAGES);
+                        TRACE(5, g);
+                        mbar_wait(&bars[AB_P_FULL + b], static_cast<uint32_t>((g >> 1) & 1), wctx, AB_P_FULL + b);
+                        TRACE(6, g);
+                        tc_fence_after();
+                        const uint32_t v_addr = smem_u32(kv_smem + s * A_STAGE_BYTES + A_KV_BYTES);
+                        const uint32_t d = tmem_base + A_COL_O + qb * A_D;
+                        const uint32_t p_tmem = tmem_base + A_COL_S + b * A_TKV;
+#pragma unroll
+                        for (int kk = 0; kk < A_TKV / 16; ++kk)
+                            mma_f16_ts(d, p_tmem + kk * 8, make_smem_desc_sw128(v_addr + kk * 2048, 16, 1024), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                        tc_commit(&bars[AB_KV_EMPTY + s]);
+                        tc_commit(&bars[AB_PV_DONE + b]);
+                        TRACE(7, g);
+                    }
+                    ++it;
+                    n = n_next;
+                    have = have_next;
                 }
             }
         } else {
             // -------------------------------------------------------------- softmax warps (one row per thread)
             const int lr = warp * 32 + lane;                 // local row = tensor-memory lane
-            const int row = q_row0 + lr;
-            const int lrb = lr / p.bm;
-            const int rb = qt * nrb + lrb;
-            const bool rb_valid = rb < nbm;
-            const int row_in_block = lr % p.bm;
-            const int part_base = rb_valid ? p.part_row_ptr[rb] : 0;
-            const uint16_t* my_table = table + lrb * ncb;
             const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-            float m_ref = -INFINITY, l_sum = 0.f;
+            const int rg = lr >> 4;                          // 16-row group inside the query tile
+            const float scale = p.scale_log2;
+            long long g = 0;
+            int it = 0;
+            // per-item values that need global loads are fetched one item ahead (no dependent-load chain at item boundaries)
+            auto item_row_base = [&](const Item& x) -> int {
+                const int r = x.qt * A_TQ + lr;
+                return (x.valid && x.n > 0 && r < p.seq_len) ? __ldg(p.part_row_ptr + (r >> p.bm_shift)) : 0;
+            };
+            auto item_codes = [&](const Item& x) -> const uint2* {
+                return reinterpret_cast<const uint2*>(plan_codes + (static_cast<size_t>(x.qt) * p.max_tiles) * 32 + rg * 4);
+            };
+            Item item = fetch_item(0, p, plan_sched);
+            int part_base_next = item_row_base(item);
+            uint2 cw_next = (item.valid && item.n > 0) ? __ldg(item_codes(item)) : make_uint2(0u, 0u);
+            for (unsigned k = 0; item.valid; ++k) {
+                const Item cur_item = item;
+                const int part_base = part_base_next;
+                uint2 cw = cw_next;                              // codes of tile 0
+                item = fetch_item(k + 1, p, plan_sched);
+                part_base_next = item_row_base(item);
+                cw_next = (item.valid && item.n > 0) ? __ldg(item_codes(item)) : make_uint2(0u, 0u);
 
-            for (int j = 0; j < n_tiles; ++j) {
-                const int b = j & 1;
-                const int tile = tile_list[j];
-                mbar_wait(&bars[AB_S_FULL + b], (j >> 1) & 1, wctx, AB_S_FULL + b);
-                tc_fence_after();
-                uint32_t raw[2][32];
-                tmem_ld32(t_lane + A_COL_S + b * A_TKV, raw[0]);
-                tmem_ld32(t_lane + A_COL_S + b * A_TKV + 32, raw[1]);
-                tc_wait_ld();
-
-                // codes of the four 16-column groups of this tile for this thread's row block
-                int code[4];
-                bool all_full = true, all_absent = true;
+                const int n = cur_item.n;
+                const int row = cur_item.qt * A_TQ + lr;
+                __half* dst = p.out + cur_item.batch * p.o_stride_b + cur_item.head * p.o_stride_h + static_cast<long long>(row) * p.o_stride_s;
+                if (n == 0) {
+                    if (row < p.seq_len) {
 #pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    const int col = tile * A_TKV + g * 16;
-                    code[g] = (rb_valid && col < p.seq_len) ? my_table[col / p.bn] : 0;
-                    all_full &= code[g] == 1;
-                    all_absent &= code[g] == 0;
+                        for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(dst + 8 * c) = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    continue;
                 }
-                const bool warp_skip = __all_sync(0xffffffffu, all_absent);
-                uint32_t packed[32];
-                if (warp_skip) {
+                const int ob = it & 1;
+                const uint2* my_codes = item_codes(cur_item);
+                const uint16_t* tl = plan_tiles + static_cast<size_t>(cur_item.qt) * p.max_tiles;
+                const int row_in_block = row & (p.bm - 1);
+                float m_ref = -INFINITY, l_sum = 0.f;
+
+                for (int j = 0; j < n; ++j, ++g) {
+                    const int b = static_cast<int>(g & 1);
+                    const uint2 cur = cw;
+                    if (j + 1 < n) cw = __ldg(my_codes + (j + 1) * 8);     // 32 codes = 64 B = 8 uint2 per tile
+                    if (threadIdx.x == 0) TRACE(0, g);
+                    mbar_wait(&bars[AB_S_FULL + b], static_cast<uint32_t>((g >> 1) & 1), wctx, AB_S_FULL + b);
+                    if (threadIdx.x == 0) TRACE(1, g);
+                    tc_fence_after();
+                    uint32_t r0[32], r1[32];
+                    tmem_ld32(t_lane + A_COL_S + b * A_TKV, r0);
+                    tmem_ld32(t_lane + A_COL_S + b * A_TKV + 32, r1);
+                    tc_wait_ld();
+                    if (threadIdx.x == 0) TRACE(2, g);
+
+                    const bool all_absent = (cur.x | cur.y) == 0u;
+                    const bool all_full = cur.x == 0x00010001u && cur.y == 0x00010001u;
+                    // the fp16 pairs of P are written over r0 as its scores are consumed
+                    if (__all_sync(0xffffffffu, all_absent)) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) packed[i] = 0u;
-                } else {
-                    float s[64];
+                        for (int i = 0; i < 32; ++i) r0[i] = 0u;
+                    } else {
+                        if (!__all_sync(0xffffffffu, all_full)) {
+                            const int tile = tl[j];
+                            const unsigned code[4] = {cur.x & 0xFFFFu, cur.x >> 16, cur.y & 0xFFFFu, cur.y >> 16};
 #pragma unroll
-                    for (int i = 0; i < 64; ++i) s[i] = __uint_as_float(raw[i >> 5][i & 31]);
-                    if (!__all_sync(0xffffffffu, all_full)) {
+                            for (int cg = 0; cg < 4; ++cg) {
+                                uint32_t* dstv = (cg < 2) ? &r0[16 * cg] : &r1[16 * (cg - 2)];
+                                if (code[cg] == 0u) {
 #pragma unroll
-                        for (int g = 0; g < 4; ++g) {
-                            if (code[g] == 0) {
+                                    for (int i = 0; i < 16; ++i) dstv[i] = 0xFF800000u;      // -inf
+                                } else if (code[cg] >= 2u) {
+                                    const int col_in_block = (tile * A_TKV + cg * 16) & (p.bn - 1);
+                                    const __half* mp = p.part_block_mask +
+                                                       ((static_cast<size_t>(part_base + code[cg] - 2) << p.bm_shift) + row_in_block) * p.bn + col_in_block;
+                                    const uint4 u0 = __ldg(reinterpret_cast<const uint4*>(mp));
+                                    const uint4 u1 = __ldg(reinterpret_cast<const uint4*>(mp + 8));
+                                    const __half2* h0 = reinterpret_cast<const __half2*>(&u0);
+                                    const __half2* h1 = reinterpret_cast<const __half2*>(&u1);
 #pragma unroll
-                                for (int i = 0; i < 16; ++i) s[16 * g + i] = -INFINITY;
-                            } else if (code[g] >= 2) {
-                                const int col_in_block = (tile * A_TKV + g * 16) % p.bn;
-                                const __half* mp = p.part_block_mask +
-                                                   (static_cast<size_t>(part_base + code[g] - 2) * p.bm + row_in_block) * p.bn + col_in_block;
-                                const uint4 u0 = __ldg(reinterpret_cast<const uint4*>(mp));
-                                const uint4 u1 = __ldg(reinterpret_cast<const uint4*>(mp + 8));
-                                const __half2* h0 = reinterpret_cast<const __half2*>(&u0);
-                                const __half2* h1 = reinterpret_cast<const __half2*>(&u1);
-#pragma unroll
-                                for (int i = 0; i < 4; ++i) {
-                                    const float2 a = __half22float2(h0[i]), c2 = __half22float2(h1[i]);
-                                    s[16 * g + 2 * i] += a.x;
-                                    s[16 * g + 2 * i + 1] += a.y;
-                                    s[16 * g + 8 + 2 * i] += c2.x;
-                                    s[16 * g + 8 + 2 * i + 1] += c2.y;
+                                    for (int i = 0; i < 4; ++i) {
+                                        const float2 a = __half22float2(h0[i]), c2 = __half22float2(h1[i]);
+                                        dstv[2 * i] = __float_as_uint(__uint_as_float(dstv[2 * i]) + a.x);
+                                        dstv[2 * i + 1] = __float_as_uint(__uint_as_float(dstv[2 * i + 1]) + a.y);
+                                        dstv[8 + 2 * i] = __float_as_uint(__uint_as_float(dstv[8 + 2 * i]) + c2.x);
+                                        dstv[8 + 2 * i + 1] = __float_as_uint(__uint_as_float(dstv[8 + 2 * i + 1]) + c2.y);
+                                    }
                                 }
                             }
                         }
-                    }
-                    float mx = -INFINITY;
+                        // row maximum of the raw scores (four independent chains), then in log2 units
+                        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-                    for (int i = 0; i < 64; ++i) {
-                        s[i] *= p.scale_log2;
-                        mx = fmaxf(mx, s[i]);
-                    }
-                    // lazy rescale: move the reference maximum only when it would grow by more than the threshold
-                    const bool need = mx > m_ref + A_RESCALE_THRESHOLD || (m_ref == -INFINITY && mx > -INFINITY);
-                    if (__any_sync(0xffffffffu, need)) {
-                        float alpha = 1.0f;
-                        if (need) {
-                            alpha = (m_ref == -INFINITY) ? 0.0f : fast_exp2(m_ref - mx);
-                            m_ref = mx;
-                            l_sum *= alpha;
+                        for (int i = 0; i < 32; i += 4) {
+                            mx0 = max3(mx0, __uint_as_float(r0[i]), __uint_as_float(r1[i]));
+                            mx1 = max3(mx1, __uint_as_float(r0[i + 1]), __uint_as_float(r1[i + 1]));
+                            mx2 = max3(mx2, __uint_as_float(r0[i + 2]), __uint_as_float(r1[i + 2]));
+                            mx3 = max3(mx3, __uint_as_float(r0[i + 3]), __uint_as_float(r1[i + 3]));
                         }
-                        if (j > 0) {
-                            mbar_wait(&bars[AB_PV_DONE + ((j - 1) & 1)], ((j - 1) >> 1) & 1, wctx, AB_PV_DONE + ((j - 1) & 1));
-                            tc_fence_after();
-                            uint32_t o[2][32];
-                            tmem_ld32(t_lane + A_COL_O, o[0]);
-                            tmem_ld32(t_lane + A_COL_O + 32, o[1]);
-                            tc_wait_ld();
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) {
-                                o[0][i] = __float_as_uint(__uint_as_float(o[0][i]) * alpha);
-                                o[1][i] = __float_as_uint(__uint_as_float(o[1][i]) * alpha);
+                        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale;
+                        // lazy rescale: move the reference maximum only when it would grow by more than the threshold
+                        const bool need = mx > m_ref + A_RESCALE_THRESHOLD || (m_ref == -INFINITY && mx > -INFINITY);
+                        if (__any_sync(0xffffffffu, need)) {
+                            float alpha = 1.0f;
+                            if (need) {
+                                alpha = (m_ref == -INFINITY) ? 0.0f : fast_exp2(m_ref - mx);
+                                m_ref = mx;
+                                l_sum *= alpha;
                             }
-                            tmem_st32(t_lane + A_COL_O, o[0]);
-                            tmem_st32(t_lane + A_COL_O + 32, o[1]);
-                            tc_wait_st();
+                            if (j > 0) {
+                                const int pb = static_cast<int>((g - 1) & 1);
+                                mbar_wait(&bars[AB_PV_DONE + pb], static_cast<uint32_t>(((g - 1) >> 1) & 1), wctx, AB_PV_DONE + pb);
+                                tc_fence_after();
+                                uint32_t o0[32], o1[32];
+                                tmem_ld32(t_lane + A_COL_O + ob * A_D, o0);
+                                tmem_ld32(t_lane + A_COL_O + ob * A_D + 32, o1);
+                                tc_wait_ld();
+#pragma unroll
+                                for (int i = 0; i < 32; ++i) {
+                                    o0[i] = __float_as_uint(__uint_as_float(o0[i]) * alpha);
+                                    o1[i] = __float_as_uint(__uint_as_float(o1[i]) * alpha);
+                                }
+                                tmem_st32(t_lane + A_COL_O + ob * A_D, o0);
+                                tmem_st32(t_lane + A_COL_O + ob * A_D + 32, o1);
+                                tc_wait_st();
+                            }
+                        }
+                        const float neg_m = (m_ref == -INFINITY) ? 0.0f : -m_ref;
+                        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+                        for (int i = 0; i < 16; i += 2) {
+                            const float a0 = fast_exp2(fmaf(__uint_as_float(r0[2 * i]), scale, neg_m));
+                            const float a1 = fast_exp2(fmaf(__uint_as_float(r0[2 * i + 1]), scale, neg_m));
+                            const float a2 = fast_exp2(fmaf(__uint_as_float(r0[2 * i + 2]), scale, neg_m));
+                            const float a3 = fast_exp2(fmaf(__uint_as_float(r0[2 * i + 3]), scale, neg_m));
+                            s0 += a0; s1 += a1; s2 += a2; s3 += a3;
+                            r0[i] = pack_half2(a0, a1);
+                            r0[i + 1] = pack_half2(a2, a3);
+                        }
+#pragma unroll
+                        for (int i = 0; i < 16; i += 2) {
+                            const float a0 = fast_exp2(fmaf(__uint_as_float(r1[2 * i]), scale, neg_m));
+                            const float a1 = fast_exp2(fmaf(__uint_as_float(r1[2 * i + 1]), scale, neg_m));
+                            const float a2 = fast_exp2(fmaf(__uint_as_float(r1[2 * i + 2]), scale, neg_m));
+                            const float a3 = fast_exp2(fmaf(__uint_as_float(r1[2 * i + 3]), scale, neg_m));
+                            s0 += a0; s1 += a1; s2 += a2; s3 += a3;
+                            r0[16 + i] = pack_half2(a0, a1);
+                            r0[16 + i + 1] = pack_half2(a2, a3);
+                        }
+                        l_sum += (s0 + s1) + (s2 + s3);
+                    }
+                    // P overlays the first 32 columns of the S buffer it was computed from; the QK^T that next writes this
+                    // buffer is issued after the PV product that reads P and the tensor core executes them in that order
+                    if (threadIdx.x == 0) TRACE(3, g);
+                    tmem_st32(t_lane + A_COL_S + b * A_TKV, r0);
+                    tc_wait_st();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars[AB_P_FULL + b]);
+                    if (threadIdx.x == 0) TRACE(4, g);
+                }
+                // ---------------------------------------------------------- item epilogue: O / l -> fp16 -> global
+                {
+                    const int pb = static_cast<int>((g - 1) & 1);
+                    mbar_wait(&bars[AB_PV_DONE + pb], static_cast<uint32_t>(((g - 1) >> 1) & 1), wctx, AB_PV_DONE + pb);
+                    tc_fence_after();
+                    uint32_t o0[32], o1[32];
+                    tmem_ld32(t_lane + A_COL_O + ob * A_D, o0);
+                    tmem_ld32(t_lane + A_COL_O + ob * A_D + 32, o1);
+                    tc_wait_ld();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars[AB_O_FREE + ob]);
+                    if (row < p.seq_len) {
+                        const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.0f;
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {
+                            const uint32_t* src = (c < 4) ? &o0[c * 8] : &o1[(c - 4) * 8];
+                            uint4 u;
+                            u.x = pack_half2(__uint_as_float(src[0]) * inv, __uint_as_float(src[1]) * inv);
+                            u.y = pack_half2(__uint_as_float(src[2]) * inv, __uint_as_float(src[3]) * inv);
+                            u.z = pack_half2(__uint_as_float(src[4]) * inv, __uint_as_float(src[5]) * inv);
+                            u.w = pack_half2(__uint_as_float(src[6]) * inv, __uint_as_float(src[7]) * inv);
+                            *reinterpret_cast<uint4*>(dst + 8 * c) = u;
                         }
                     }
-                    const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
-                    float sum = 0.f;
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const float e0 = fast_exp2(s[2 * i] - m_use), e1 = fast_exp2(s[2 * i + 1] - m_use);
-                        sum += e0 + e1;
-                        packed[i] = pack_half2(e0, e1);
-                    }
-                    l_sum += sum;
                 }
-                // P buffer b is free once the PV product of tile j-2 has completed
-                if (j >= 2) mbar_wait(&bars[AB_PV_DONE + b], ((j - 2) >> 1) & 1, wctx, AB_PV_DONE + b);
-                tc_fence_after();
-                tmem_st32(t_lane + A_COL_P + b * (A_TKV / 2), packed);
-                tc_wait_st();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bars[AB_P_FULL + b]);
+                ++it;
             }
-            // ---------------------------------------------------------- epilogue: O / l -> fp16 -> global
-            const int last = n_tiles - 1;
-            mbar_wait(&bars[AB_PV_DONE + (last & 1)], (last >> 1) & 1, wctx, AB_PV_DONE + (last & 1));
-            tc_fence_after();
-            uint32_t o[2][32];
-            tmem_ld32(t_lane + A_COL_O, o[0]);
-            tmem_ld32(t_lane + A_COL_O + 32, o[1]);
-            tc_wait_ld();
-            if (row < p.seq_len) {
-                const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.0f;
-                __half* dst = p.out + batch * p.o_stride_b + head * p.o_stride_h + static_cast<long long>(row) * p.o_stride_s;
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const uint32_t* src = &o[c >> 2][(c & 3) * 8];
-                    uint4 u;
-                    u.x = pack_half2(__uint_as_float(src[0]) * inv, __uint_as_float(src[1]) * inv);
-                    u.y = pack_half2(__uint_as_float(src[2]) * inv, __uint_as_float(src[3]) * inv);
-                    u.z = pack_half2(__uint_as_float(src[4]) * inv, __uint_as_float(src[5]) * inv);
-                    u.w = pack_half2(__uint_as_float(src[6]) * inv, __uint_as_float(src[7]) * inv);
-                    *reinterpret_cast<uint4*>(dst + 8 * c) = u;
-                }
-            }
-        }
-    } else if (n_tiles == 0 && warp < 4) {
-        // no listed key for any of these rows: the output is zero
-        const int row = q_row0 + warp * 32 + lane;
-        if (row < p.seq_len) {
-            __half* dst = p.out + batch * p.o_stride_b + head * p.o_stride_h + static_cast<long long>(row) * p.o_stride_s;
-#pragma unroll
-            for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(dst + 8 * c) = make_uint4(0u, 0u, 0u, 0u);
         }
     }
     tc_fence_before();
@@ -357,17 +572,12 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     }
 }
 
-size_t attn_smem_bytes(int seq_len, int bm, int bn) {
-    const int n_kv_tiles_all = (seq_len + A_TKV - 1) / A_TKV;
-    const size_t table = static_cast<size_t>(A_TQ / bm) * (seq_len / bn) * 2;
-    return 1024 + A_Q_BYTES + static_cast<size_t>(A_STAGES) * A_STAGE_BYTES + AB_COUNT * 8 + 16 +
-           static_cast<size_t>((n_kv_tiles_all + 7) & ~7) * 2 + table + 16;
-}
+constexpr size_t A_SMEM_BYTES = 1024 + 2 * A_Q_BYTES + static_cast<size_t>(A_STAGES) * A_STAGE_BYTES + AB_COUNT * 8 + 16;
 
 // Sorts the three outer dimensions (row, head, batch) by stride so that the tensor map's strides ascend;
 // returns the coordinate slot of each logical dimension.
-int make_qkv_map(CUtensorMap* map, const void* base, int batch, int heads, int seq_len, const long long st[3], int box_rows, int slot_s[1],
-                 int slot_h[1], int slot_b[1]) {
+int make_qkv_map(CUtensorMap* map, const void* base, int batch, int heads, int seq_len, const long long st[3], int box_rows, int* slot_s,
+                 int* slot_h, int* slot_b) {
     struct Dim { uint64_t size; long long stride; int logical; } d[3] = {
         {static_cast<uint64_t>(seq_len), st[2], 0}, {static_cast<uint64_t>(heads), st[1], 1}, {static_cast<uint64_t>(batch), st[0], 2}};
     for (int i = 0; i < 3; ++i)
@@ -385,28 +595,88 @@ int make_qkv_map(CUtensorMap* map, const void* base, int batch, int heads, int s
     return make_tensor_map_f16(map, base, 4, dims, strides, box);
 }
 
+int log2_exact(int v) {
+    int s = 0;
+    while ((1 << s) < v) ++s;
+    return s;
+}
+
+int check_blocks(int seq_len, int block_m, int block_n) {
+    STOF_REQUIRE(seq_len > 0, "block_attn: bad seq_len");
+    STOF_REQUIRE(block_m == 16 || block_m == 32 || block_m == 64 || block_m == 128, "block_attn: BLOCK_M %d not in {16,32,64,128}", block_m);
+    STOF_REQUIRE(block_n == 16 || block_n == 32 || block_n == 64 || block_n == 128, "block_attn: BLOCK_N %d not in {16,32,64,128}", block_n);
+    STOF_REQUIRE(seq_len % block_m == 0 && seq_len % block_n == 0, "block_attn: seq_len %d not a multiple of BLOCK_M %d / BLOCK_N %d", seq_len,
+                 block_m, block_n);
+    const size_t table_bytes = static_cast<size_t>(A_TQ / block_m) * (seq_len / block_n) * 2;
+    if (table_bytes > A_MAX_TABLE_BYTES) {
+        set_error("block_attn: seq_len %d with %dx%d blocks needs a %zu-byte block table, beyond the maximum of %d", seq_len, block_m, block_n,
+                  table_bytes, A_MAX_TABLE_BYTES);
+        return STOF_E_LIMIT;
+    }
+    return STOF_OK;
+}
+
 }  // namespace
 }  // namespace stof
 
 using namespace stof;
 
+#ifdef STOF_TRACE
+long long* g_trace_ptr = nullptr;
+extern "C" int stof_trace_read(long long* host, int n) {
+    cudaDeviceSynchronize();
+    return static_cast<int>(cudaMemcpy(host, g_trace_ptr, n * sizeof(long long), cudaMemcpyDeviceToHost));
+}
+#endif
+
+extern "C" size_t stof_block_attn_plan_bytes(int seq_len, int block_m, int block_n) {
+    if (seq_len <= 0 || block_m <= 0 || block_n <= 0) return 0;
+    const int nqt = (seq_len + A_TQ - 1) / A_TQ, maxt = (seq_len + A_TKV - 1) / A_TKV;
+    return plan_total_bytes(nqt, maxt) + 16;          // trailing 16 bytes: the ticket of the plan kernel
+}
+
+extern "C" int stof_block_attn_plan(const int* full_row_ptr, const int* full_col_idx, const int* part_row_ptr, const int* part_col_idx,
+                                    int seq_len, int block_m, int block_n, void* plan, size_t plan_bytes, int* status_dev, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (int rc = check_blocks(seq_len, block_m, block_n)) return rc;
+    STOF_REQUIRE(full_row_ptr && part_row_ptr && plan, "block_attn_plan: null pointer");
+    STOF_REQUIRE(aligned16(plan), "block_attn_plan: plan buffer must be 16-byte aligned");
+    const size_t need = stof_block_attn_plan_bytes(seq_len, block_m, block_n);
+    if (plan_bytes < need) {
+        set_error("block_attn_plan: plan buffer of %zu bytes, need %zu", plan_bytes, need);
+        return STOF_E_WORKSPACE;
+    }
+    const int nqt = (seq_len + A_TQ - 1) / A_TQ, maxt = (seq_len + A_TKV - 1) / A_TKV;
+    unsigned char* pl = static_cast<unsigned char*>(plan);
+    unsigned int* ticket = reinterpret_cast<unsigned int*>(pl + plan_total_bytes(nqt, maxt));
+    STOF_CUDA(cudaMemsetAsync(pl, 0, sizeof(PlanHeader), stream));
+    STOF_CUDA(cudaMemsetAsync(ticket, 0, 16, stream));
+    const size_t smem = static_cast<size_t>(A_TQ / block_m) * (seq_len / block_n) * 2;
+    static bool configured[64] = {};
+    int dev = 0;
+    STOF_CUDA(cudaGetDevice(&dev));
+    if (smem > 40 * 1024 && (dev < 0 || dev >= 64 || !configured[dev])) {
+        STOF_CUDA(cudaFuncSetAttribute(plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, A_MAX_TABLE_BYTES));
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    plan_kernel<<<nqt, 256, smem, stream>>>(full_row_ptr, full_col_idx, part_row_ptr, part_col_idx, seq_len, block_m, block_n, pl, ticket, status_dev);
+    STOF_CUDA(cudaGetLastError());
+    return STOF_OK;
+}
+
 extern "C" int stof_block_attn(const void* q, const void* k, const void* v, void* out, int batch, int heads, int seq_len, int head_dim,
                                const long long q_strides[3], const long long k_strides[3], const long long v_strides[3],
-                               const long long out_strides[3], const int* full_row_ptr, const int* full_col_idx, const int* part_row_ptr,
-                               const int* part_col_idx, const void* part_block_mask, const int* load_row_ptr, const int* load_col_idx,
+                               const long long out_strides[3], const int* part_row_ptr, const void* part_block_mask, const void* plan,
                                int block_m, int block_n, int num_warps, float softmax_scale, int* status_dev, void* stream_) {
-    (void)load_row_ptr; (void)load_col_idx; (void)num_warps;
+    (void)num_warps;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     STOF_REQUIRE(q && k && v && out, "block_attn: null q/k/v/out");
-    STOF_REQUIRE(full_row_ptr && part_row_ptr, "block_attn: null row pointer array");
+    STOF_REQUIRE(part_row_ptr && plan, "block_attn: null part_row_ptr or plan");
     STOF_REQUIRE(head_dim == A_D, "block_attn: head_dim %d unsupported (the kernels are built for 64, as the reference's are)", head_dim);
-    STOF_REQUIRE(batch > 0 && heads > 0 && seq_len > 0, "block_attn: bad shape");
-    STOF_REQUIRE(batch <= 65535 && heads <= 65535, "block_attn: batch/heads beyond 65535");
-    STOF_REQUIRE(block_m == 16 || block_m == 32 || block_m == 64 || block_m == 128, "block_attn: BLOCK_M %d not in {16,32,64,128}", block_m);
-    STOF_REQUIRE(block_n == 16 || block_n == 32 || block_n == 64 || block_n == 128, "block_attn: BLOCK_N %d not in {16,32,64,128}", block_n);
-    STOF_REQUIRE(seq_len % block_m == 0 && seq_len % block_n == 0, "block_attn: seq_len %d not a multiple of BLOCK_M %d / BLOCK_N %d", seq_len,
-                 block_m, block_n);
-    STOF_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out) && aligned16(part_block_mask),
+    STOF_REQUIRE(batch > 0 && heads > 0, "block_attn: bad shape");
+    if (int rc = check_blocks(seq_len, block_m, block_n)) return rc;
+    STOF_REQUIRE(softmax_scale > 0.f, "block_attn: softmax_scale must be positive");
+    STOF_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out) && aligned16(part_block_mask) && aligned16(plan),
                  "block_attn: pointers must be 16-byte aligned");
     const long long* all[4] = {q_strides, k_strides, v_strides, out_strides};
     for (int t = 0; t < 4; ++t) {
@@ -414,36 +684,47 @@ extern "C" int stof_block_attn(const void* q, const void* k, const void* v, void
         for (int i = 0; i < 3; ++i)
             STOF_REQUIRE(all[t][i] > 0 && all[t][i] % 8 == 0, "block_attn: strides must be positive multiples of 8 elements");
     }
-    const size_t table_bytes = static_cast<size_t>(A_TQ / block_m) * (seq_len / block_n) * 2;
-    if (table_bytes > A_MAX_TABLE_BYTES) {
-        set_error("block_attn: seq_len %d with %dx%d blocks needs a %zu-byte block table, beyond the maximum of %d", seq_len, block_m, block_n,
-                  table_bytes, A_MAX_TABLE_BYTES);
-        return STOF_E_LIMIT;
-    }
     AttnParams p;
     p.out = static_cast<__half*>(out);
     p.o_stride_b = out_strides[0]; p.o_stride_h = out_strides[1]; p.o_stride_s = out_strides[2];
-    p.full_row_ptr = full_row_ptr; p.full_col_idx = full_col_idx;
-    p.part_row_ptr = part_row_ptr; p.part_col_idx = part_col_idx;
+    p.part_row_ptr = part_row_ptr;
     p.part_block_mask = static_cast<const __half*>(part_block_mask);
+    p.plan = static_cast<const unsigned char*>(plan);
     p.batch = batch; p.heads = heads; p.seq_len = seq_len; p.bm = block_m; p.bn = block_n;
+    p.bm_shift = log2_exact(block_m); p.bn_shift = log2_exact(block_n);
+    p.n_qtiles = (seq_len + A_TQ - 1) / A_TQ;
+    p.max_tiles = (seq_len + A_TKV - 1) / A_TKV;
     p.scale_log2 = softmax_scale * 1.4426950408889634f;
     p.status = status_dev;
+    const long long items = static_cast<long long>(batch) * heads * p.n_qtiles;
+    STOF_REQUIRE(items < (1ll << 31), "block_attn: batch * heads * query tiles beyond 2^31");
+    p.total_items = static_cast<unsigned>(items);
+    p.bh_total = static_cast<unsigned>(batch) * static_cast<unsigned>(heads);
+#ifdef STOF_TRACE
+    {
+        static long long* trace_buf = nullptr;
+        if (!trace_buf) cudaMalloc(&trace_buf, 256 * 8 * sizeof(long long));
+        cudaMemsetAsync(trace_buf, 0, 256 * 8 * sizeof(long long), stream);
+        p.trace = trace_buf;
+        extern long long* g_trace_ptr;
+        g_trace_ptr = trace_buf;
+    }
+#endif
     CUtensorMap mq, mk, mv;
     if (int rc = make_qkv_map(&mq, q, batch, heads, seq_len, q_strides, A_TQ, &p.slot_s[0], &p.slot_h[0], &p.slot_b[0])) return rc;
     if (int rc = make_qkv_map(&mk, k, batch, heads, seq_len, k_strides, A_TKV, &p.slot_s[1], &p.slot_h[1], &p.slot_b[1])) return rc;
     if (int rc = make_qkv_map(&mv, v, batch, heads, seq_len, v_strides, A_TKV, &p.slot_s[2], &p.slot_h[2], &p.slot_b[2])) return rc;
 
-    const size_t smem = attn_smem_bytes(seq_len, block_m, block_n);
-    const dim3 grid((seq_len + A_TQ - 1) / A_TQ, heads, batch);
-    static size_t configured_smem[64] = {};
+    static bool configured[64] = {};
     int dev = 0;
     STOF_CUDA(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64 || configured_smem[dev] < smem) {
-        STOF_CUDA(cudaFuncSetAttribute(block_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-        if (dev >= 0 && dev < 64) configured_smem[dev] = smem;
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        STOF_CUDA(cudaFuncSetAttribute(block_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(A_SMEM_BYTES)));
+        if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    block_attn_kernel<<<grid, A_THREADS, smem, stream>>>(mq, mk, mv, p);
+    long long grid = static_cast<long long>(A_CTAS_PER_SM) * sm_count();
+    if (grid > items) grid = items;
+    block_attn_kernel<<<static_cast<unsigned>(grid), A_THREADS, A_SMEM_BYTES, stream>>>(mq, mk, mv, p);
     STOF_CUDA(cudaGetLastError());
     return STOF_OK;
 }

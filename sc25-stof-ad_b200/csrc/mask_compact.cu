@@ -8,7 +8,7 @@
 // Phase 1 (classify_kernel): the mask is streamed once with 128-bit loads.  A thread block owns a
 // stripe of one block-row by a run of whole tiles, keeps two byte flags per tile in shared memory
 // (saw-a-non-one / saw-a-non-zero) and writes one class byte per tile.  The last block to finish
-// (atomic ticket) turns the class bytes into per-row counts with warp ballots and into the three
+// (atomic ticket) turns the class bytes into per-row counts (independent loads + shared-memory atomics) and into the three
 // row-pointer arrays with a warp-shuffle prefix sum.
 // Phase 2 (fill_kernel): one warp per block-row ranks its tiles with ballots + popc to place the
 // column indices; the partial tiles of the row are then gathered by the whole thread block.
@@ -67,24 +67,17 @@ __device__ void scan_rows(const unsigned char* cls, int nbm, int nbn, int* full_
         part_row_ptr[0] = 0;
         load_row_ptr[0] = 0;
     }
-    // rows are processed in chunks of 32 * nwarps; inside a chunk one warp counts 32 rows' tiles, then warp 0 scans
+    // rows are processed in chunks of 32 * nwarps: every thread loads class bytes of the chunk independently
+    // (no serial chain of dependent loads) and counts into shared memory, then warp 0 scans the chunk
     const int chunk = 32 * nwarps;
     for (int r0 = 0; r0 < nbm; r0 += chunk) {
-        for (int rr = 0; rr < 32; ++rr) {
-            const int r = r0 + warp * 32 + rr;
-            int nf = 0, np = 0;
-            if (r < nbm) {
-                for (int c0 = 0; c0 < nbn; c0 += 32) {
-                    const int c = c0 + lane;
-                    const int k = c < nbn ? __ldcg(cls + static_cast<size_t>(r) * nbn + c) : CLS_EMPTY;
-                    nf += __popc(__ballot_sync(0xffffffffu, k == CLS_FULL));
-                    np += __popc(__ballot_sync(0xffffffffu, k == CLS_PART));
-                }
-            }
-            if (lane == 0) {
-                row_counts[2 * (warp * 32 + rr)] = nf;
-                row_counts[2 * (warp * 32 + rr) + 1] = np;
-            }
+        for (int i = threadIdx.x; i < 2 * chunk; i += blockDim.x) row_counts[i] = 0;
+        __syncthreads();
+        const int rows_here = min(chunk, nbm - r0);
+        const long long cells = static_cast<long long>(rows_here) * nbn;
+        for (long long i = threadIdx.x; i < cells; i += blockDim.x) {
+            const int k = __ldcg(cls + static_cast<size_t>(r0) * nbn + i);
+            if (k != CLS_EMPTY) atomicAdd(&row_counts[2 * static_cast<int>(i / nbn) + (k == CLS_PART ? 1 : 0)], 1);
         }
         __syncthreads();
         if (warp == 0) {

@@ -49,12 +49,17 @@ def test_argument_validation_needs_no_gpu(built_lib):
     from stof_b200 import _lib
     s3 = _lib.strides3((64, 64, 64))
     one = ctypes.c_void_p(16)
-    rc = L.stof_block_attn(one, one, one, one, 1, 1, 64, 32, s3, s3, s3, s3, one, one, one, one, None, None, None, 64, 64, 4, 0.125, None, None)
+    rc = L.stof_block_attn(one, one, one, one, 1, 1, 64, 32, s3, s3, s3, s3, one, None, one, 64, 64, 4, 0.125, None, None)
     assert rc == -1 and b"head_dim" in L.stof_last_error()
-    rc = L.stof_block_attn(one, one, one, one, 1, 1, 100, 64, s3, s3, s3, s3, one, one, one, one, None, None, None, 64, 64, 4, 0.125, None, None)
+    rc = L.stof_block_attn(one, one, one, one, 1, 1, 100, 64, s3, s3, s3, s3, one, None, one, 64, 64, 4, 0.125, None, None)
     assert rc == -1 and b"multiple" in L.stof_last_error()
-    rc = L.stof_block_attn(one, one, one, one, 1, 1, 96, 64, s3, s3, s3, s3, one, one, one, one, None, None, None, 48, 48, 4, 0.125, None, None)
+    rc = L.stof_block_attn(one, one, one, one, 1, 1, 96, 64, s3, s3, s3, s3, one, None, one, 48, 48, 4, 0.125, None, None)
     assert rc == -1 and b"BLOCK_M" in L.stof_last_error()
+    rc = L.stof_block_attn_plan(one, one, one, one, 128, 64, 64, one, 8, None, None)
+    assert rc == -3 and b"plan buffer" in L.stof_last_error()
+    rc = L.stof_block_attn_plan(one, one, one, one, 65536, 16, 16, one, 1 << 30, None, None)
+    assert rc == -4 and b"block table" in L.stof_last_error()
+    assert L.stof_block_attn_plan_bytes(2048, 64, 64) > 16 * 32 * 66
     rc = L.stof_mask_classify(one, 0, 1, 100, 64, 64, one, one, one, one, one, 1 << 20, None)
     assert rc == -1
     rc = L.stof_mask_classify(one, 0, 1, 128, 64, 64, one, one, one, one, one, 8, None)
