@@ -25,16 +25,23 @@ namespace stof {
 namespace {
 
 constexpr int A_TQ = 128, A_TKV = 64, A_D = 64;
-constexpr int A_STAGES = 4;
+constexpr int A_STAGES = 3;
 constexpr int A_Q_BYTES = A_TQ * A_D * 2;         // 16 KB per Q buffer
 constexpr int A_KV_BYTES = A_TKV * A_D * 2;       // 8 KB each for K and V
 constexpr int A_STAGE_BYTES = 2 * A_KV_BYTES;
+constexpr int A_OSTAGE_BYTES = 32 * A_D * 2;     // 4 KB output staging per softmax warp (TMA store source)
 constexpr int A_THREADS = 192;
-constexpr int A_CTAS_PER_SM = 2;
+#ifndef A_CTAS
+#define A_CTAS 2
+#endif
+constexpr int A_CTAS_PER_SM = A_CTAS;
 constexpr int A_TMEM_COLS = 256;
 constexpr int A_COL_S = 0, A_COL_O = 128;         // S0 @0, S1 @64 (P overlays the first 32 columns of its S), O0 @128, O1 @192
 constexpr int A_MAX_TABLE_BYTES = 48 * 1024;
 constexpr float A_RESCALE_THRESHOLD = 8.0f;       // log2 units
+#ifndef A_POLY_PAIRS
+#define A_POLY_PAIRS 2                            // of every 8 column pairs, this many take the polynomial exp2
+#endif
 constexpr int A_GROUP_BH = 40;                    // (batch, head) pairs per scheduling group: 40 x 2 x S x 128 B of K/V stay in L2
 
 enum {
@@ -160,8 +167,6 @@ plan_kernel(const int* __restrict__ full_row_ptr, const int* __restrict__ full_c
 // Attention kernel
 // ---------------------------------------------------------------------------------------------
 struct AttnParams {
-    __half* out;
-    long long o_stride_b, o_stride_h, o_stride_s;
     const int* part_row_ptr;
     const __half* part_block_mask;
     const unsigned char* plan;
@@ -169,7 +174,7 @@ struct AttnParams {
     int bm, bn, bm_shift, bn_shift;
     int n_qtiles, max_tiles;
     unsigned total_items, bh_total;
-    int slot_s[3], slot_h[3], slot_b[3];   // coordinate slot (1..3) of row / head / batch in the q, k, v tensor maps
+    int slot_s[4], slot_h[4], slot_b[4];   // coordinate slot (1..3) of row / head / batch in the q, k, v, out tensor maps
     float scale_log2;
     int* status;
 #ifdef STOF_TRACE
@@ -182,6 +187,13 @@ __device__ __forceinline__ void tma_tile(void* dst, const CUtensorMap* map, uint
     const int c2 = ss == 2 ? row : (sh == 2 ? h : b);
     const int c3 = ss == 3 ? row : (sh == 3 ? h : b);
     tma_load_4d(dst, map, bar, 0, c1, c2, c3);
+}
+
+__device__ __forceinline__ void tma_tile_store(const CUtensorMap* map, const void* src, int row, int h, int b, int ss, int sh, int sb) {
+    const int c1 = ss == 1 ? row : (sh == 1 ? h : b);
+    const int c2 = ss == 2 ? row : (sh == 2 ? h : b);
+    const int c3 = ss == 3 ? row : (sh == 3 ? h : b);
+    tma_store_4d(map, src, 0, c1, c2, c3);
 }
 
 // Static schedule: items are enumerated group by group ((batch, head) pairs in chunks of A_GROUP_BH), inside a
@@ -217,16 +229,21 @@ __device__ __forceinline__ Item fetch_item(unsigned k, const AttnParams& p, cons
 #define TRACE(slot, step) do { } while (0)
 #endif
 
-__device__ __forceinline__ float max3(float a, float b, float c) { return fmaxf(a, fmaxf(b, c)); }
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 
 __global__ void __launch_bounds__(A_THREADS, A_CTAS_PER_SM)
 block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                  const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
+                  const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o, const AttnParams p) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     unsigned char* q_smem = smem;                                   // 2 buffers
     unsigned char* kv_smem = q_smem + 2 * A_Q_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(kv_smem + A_STAGES * A_STAGE_BYTES);
+    unsigned char* o_smem = kv_smem + A_STAGES * A_STAGE_BYTES;      // 4 x 4 KB, one slab per softmax warp
+    uint64_t* bars = reinterpret_cast<uint64_t*>(o_smem + 4 * A_OSTAGE_BYTES);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + AB_COUNT);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -387,25 +404,43 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             auto item_codes = [&](const Item& x) -> const uint2* {
                 return reinterpret_cast<const uint2*>(plan_codes + (static_cast<size_t>(x.qt) * p.max_tiles) * 32 + rg * 4);
             };
+            unsigned char* slab = o_smem + warp * A_OSTAGE_BYTES;       // this warp's 32 x 128 B output staging (1024-aligned)
+            // writes one fp16 output row (8 x 16 B) into the slab in the 128-byte-swizzled layout of the output tensor map,
+            // then one lane hands the slab to the TMA store; rows beyond the sequence end are clipped by the tensor map
+            auto store_rows = [&](const uint4 (&u)[8], const Item& x) {
+                if (lane == 0) tma_store_wait_read();                    // the previous store has finished reading the slab
+                __syncwarp();
+#pragma unroll
+                for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(slab + lane * 128 + ((c ^ (lane & 7)) << 4)) = u[c];
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    tma_tile_store(&map_o, slab, x.qt * A_TQ + warp * 32, x.head, x.batch, p.slot_s[3], p.slot_h[3], p.slot_b[3]);
+                    tma_store_commit();
+                }
+            };
+            // two-deep item pipeline: the schedule entry of item k+2 and the row-dependent loads of item k+1 are in flight
+            // while item k is processed
             Item item = fetch_item(0, p, plan_sched);
+            Item item2 = fetch_item(1, p, plan_sched);
             int part_base_next = item_row_base(item);
             uint2 cw_next = (item.valid && item.n > 0) ? __ldg(item_codes(item)) : make_uint2(0u, 0u);
             for (unsigned k = 0; item.valid; ++k) {
                 const Item cur_item = item;
                 const int part_base = part_base_next;
                 uint2 cw = cw_next;                              // codes of tile 0
-                item = fetch_item(k + 1, p, plan_sched);
+                item = item2;
                 part_base_next = item_row_base(item);
                 cw_next = (item.valid && item.n > 0) ? __ldg(item_codes(item)) : make_uint2(0u, 0u);
+                item2 = fetch_item(k + 2, p, plan_sched);
 
                 const int n = cur_item.n;
                 const int row = cur_item.qt * A_TQ + lr;
-                __half* dst = p.out + cur_item.batch * p.o_stride_b + cur_item.head * p.o_stride_h + static_cast<long long>(row) * p.o_stride_s;
                 if (n == 0) {
-                    if (row < p.seq_len) {
+                    uint4 z[8];
 #pragma unroll
-                        for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(dst + 8 * c) = make_uint4(0u, 0u, 0u, 0u);
-                    }
+                    for (int c = 0; c < 8; ++c) z[c] = make_uint4(0u, 0u, 0u, 0u);
+                    store_rows(z, cur_item);
                     continue;
                 }
                 const int ob = it & 1;
@@ -430,99 +465,125 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 
                     const bool all_absent = (cur.x | cur.y) == 0u;
                     const bool all_full = cur.x == 0x00010001u && cur.y == 0x00010001u;
-                    // the fp16 pairs of P are written over r0 as its scores are consumed
+
+                    // P = 2^(s * scale - m) for the 64 scores in r0/r1: pairs of columns with packed fp32 FMAs; A_POLY_PAIRS of
+                    // every 8 pairs take the FMA-pipe polynomial instead of the MUFU unit.  The fp16 pairs of P are written over
+                    // r0 as its scores are consumed.  Returns the row sum of this tile.
+                    auto exp_tile = [&](float neg_m) -> float {
+                        const uint64_t scale2 = pk2(scale, scale), negm2 = pk2(neg_m, neg_m);
+                        uint64_t sum_a = pk2(0.f, 0.f), sum_b = pk2(0.f, 0.f);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const uint32_t lo = (i < 16) ? r0[2 * i] : r1[2 * (i - 16)];
+                            const uint32_t hi = (i < 16) ? r0[2 * i + 1] : r1[2 * (i - 16) + 1];
+                            const uint64_t x2 = fma2(pk2(__uint_as_float(lo), __uint_as_float(hi)), scale2, negm2);
+                            float e0, e1;
+                            if ((i & 7) < A_POLY_PAIRS) {
+                                exp2_poly_pair(x2, e0, e1);
+                            } else {
+                                float x0, x1;
+                                upk2(x2, x0, x1);
+                                e0 = fast_exp2(x0);
+                                e1 = fast_exp2(x1);
+                            }
+                            if (i & 1) sum_b = add2(sum_b, pk2(e0, e1));
+                            else sum_a = add2(sum_a, pk2(e0, e1));
+                            r0[i] = pack_half2(e0, e1);          // pair i of P; r0[2i], r0[2i+1] were consumed above
+                        }
+                        float sa0, sa1;
+                        upk2(add2(sum_a, sum_b), sa0, sa1);
+                        return sa0 + sa1;
+                    };
+
                     if (__all_sync(0xffffffffu, all_absent)) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i) r0[i] = 0u;
                     } else {
-                        if (!__all_sync(0xffffffffu, all_full)) {
-                            const int tile = tl[j];
-                            const unsigned code[4] = {cur.x & 0xFFFFu, cur.x >> 16, cur.y & 0xFFFFu, cur.y >> 16};
+                        const bool warp_full = __all_sync(0xffffffffu, all_full);
+                        // Speculative step: a fully listed tile is exponentiated against the current reference maximum without
+                        // a maximum pass.  It stands if every row sum stays below 2^8 (no exponent beyond the lazy-rescale
+                        // threshold can hide in such a sum; infinities and NaNs fail the test too); otherwise the scores are
+                        // read again and the exact path below runs.
+                        bool done = false;
+                        if (warp_full && j > 0 && __all_sync(0xffffffffu, m_ref != -INFINITY)) {
+                            const float tile_sum = exp_tile(-m_ref);
+                            if (__all_sync(0xffffffffu, tile_sum <= 256.0f)) {
+                                l_sum += tile_sum;
+                                done = true;
+                            } else {
+                                tmem_ld32(t_lane + A_COL_S + b * A_TKV, r0);
+                                tmem_ld32(t_lane + A_COL_S + b * A_TKV + 32, r1);
+                                tc_wait_ld();
+                            }
+                        }
+                        if (!done) {
+                            if (!warp_full) {
+                                const int tile = tl[j];
+                                const unsigned code[4] = {cur.x & 0xFFFFu, cur.x >> 16, cur.y & 0xFFFFu, cur.y >> 16};
 #pragma unroll
-                            for (int cg = 0; cg < 4; ++cg) {
-                                uint32_t* dstv = (cg < 2) ? &r0[16 * cg] : &r1[16 * (cg - 2)];
-                                if (code[cg] == 0u) {
+                                for (int cg = 0; cg < 4; ++cg) {
+                                    uint32_t* dstv = (cg < 2) ? &r0[16 * cg] : &r1[16 * (cg - 2)];
+                                    if (code[cg] == 0u) {
 #pragma unroll
-                                    for (int i = 0; i < 16; ++i) dstv[i] = 0xFF800000u;      // -inf
-                                } else if (code[cg] >= 2u) {
-                                    const int col_in_block = (tile * A_TKV + cg * 16) & (p.bn - 1);
-                                    const __half* mp = p.part_block_mask +
-                                                       ((static_cast<size_t>(part_base + code[cg] - 2) << p.bm_shift) + row_in_block) * p.bn + col_in_block;
-                                    const uint4 u0 = __ldg(reinterpret_cast<const uint4*>(mp));
-                                    const uint4 u1 = __ldg(reinterpret_cast<const uint4*>(mp + 8));
-                                    const __half2* h0 = reinterpret_cast<const __half2*>(&u0);
-                                    const __half2* h1 = reinterpret_cast<const __half2*>(&u1);
+                                        for (int i = 0; i < 16; ++i) dstv[i] = 0xFF800000u;      // -inf
+                                    } else if (code[cg] >= 2u) {
+                                        const int col_in_block = (tile * A_TKV + cg * 16) & (p.bn - 1);
+                                        const __half* mp = p.part_block_mask +
+                                                           ((static_cast<size_t>(part_base + code[cg] - 2) << p.bm_shift) + row_in_block) * p.bn + col_in_block;
+                                        const uint4 u0 = __ldg(reinterpret_cast<const uint4*>(mp));
+                                        const uint4 u1 = __ldg(reinterpret_cast<const uint4*>(mp + 8));
+                                        const __half2* h0 = reinterpret_cast<const __half2*>(&u0);
+                                        const __half2* h1 = reinterpret_cast<const __half2*>(&u1);
 #pragma unroll
-                                    for (int i = 0; i < 4; ++i) {
-                                        const float2 a = __half22float2(h0[i]), c2 = __half22float2(h1[i]);
-                                        dstv[2 * i] = __float_as_uint(__uint_as_float(dstv[2 * i]) + a.x);
-                                        dstv[2 * i + 1] = __float_as_uint(__uint_as_float(dstv[2 * i + 1]) + a.y);
-                                        dstv[8 + 2 * i] = __float_as_uint(__uint_as_float(dstv[8 + 2 * i]) + c2.x);
-                                        dstv[8 + 2 * i + 1] = __float_as_uint(__uint_as_float(dstv[8 + 2 * i + 1]) + c2.y);
+                                        for (int i = 0; i < 4; ++i) {
+                                            const float2 a = __half22float2(h0[i]), c2 = __half22float2(h1[i]);
+                                            dstv[2 * i] = __float_as_uint(__uint_as_float(dstv[2 * i]) + a.x);
+                                            dstv[2 * i + 1] = __float_as_uint(__uint_as_float(dstv[2 * i + 1]) + a.y);
+                                            dstv[8 + 2 * i] = __float_as_uint(__uint_as_float(dstv[8 + 2 * i]) + c2.x);
+                                            dstv[8 + 2 * i + 1] = __float_as_uint(__uint_as_float(dstv[8 + 2 * i + 1]) + c2.y);
+                                        }
                                     }
                                 }
                             }
-                        }
-                        // row maximum of the raw scores (four independent chains), then in log2 units
-                        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+                            // row maximum of the raw scores (four independent chains of 3-input maxima), then in log2 units
+                            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-                        for (int i = 0; i < 32; i += 4) {
-                            mx0 = max3(mx0, __uint_as_float(r0[i]), __uint_as_float(r1[i]));
-                            mx1 = max3(mx1, __uint_as_float(r0[i + 1]), __uint_as_float(r1[i + 1]));
-                            mx2 = max3(mx2, __uint_as_float(r0[i + 2]), __uint_as_float(r1[i + 2]));
-                            mx3 = max3(mx3, __uint_as_float(r0[i + 3]), __uint_as_float(r1[i + 3]));
-                        }
-                        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale;
-                        // lazy rescale: move the reference maximum only when it would grow by more than the threshold
-                        const bool need = mx > m_ref + A_RESCALE_THRESHOLD || (m_ref == -INFINITY && mx > -INFINITY);
-                        if (__any_sync(0xffffffffu, need)) {
-                            float alpha = 1.0f;
-                            if (need) {
-                                alpha = (m_ref == -INFINITY) ? 0.0f : fast_exp2(m_ref - mx);
-                                m_ref = mx;
-                                l_sum *= alpha;
+                            for (int i = 0; i < 32; i += 4) {
+                                mx0 = max3(mx0, __uint_as_float(r0[i]), __uint_as_float(r1[i]));
+                                mx1 = max3(mx1, __uint_as_float(r0[i + 1]), __uint_as_float(r1[i + 1]));
+                                mx2 = max3(mx2, __uint_as_float(r0[i + 2]), __uint_as_float(r1[i + 2]));
+                                mx3 = max3(mx3, __uint_as_float(r0[i + 3]), __uint_as_float(r1[i + 3]));
                             }
-                            if (j > 0) {
-                                const int pb = static_cast<int>((g - 1) & 1);
-                                mbar_wait(&bars[AB_PV_DONE + pb], static_cast<uint32_t>(((g - 1) >> 1) & 1), wctx, AB_PV_DONE + pb);
-                                tc_fence_after();
-                                uint32_t o0[32], o1[32];
-                                tmem_ld32(t_lane + A_COL_O + ob * A_D, o0);
-                                tmem_ld32(t_lane + A_COL_O + ob * A_D + 32, o1);
-                                tc_wait_ld();
-#pragma unroll
-                                for (int i = 0; i < 32; ++i) {
-                                    o0[i] = __float_as_uint(__uint_as_float(o0[i]) * alpha);
-                                    o1[i] = __float_as_uint(__uint_as_float(o1[i]) * alpha);
+                            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale;
+                            // lazy rescale: move the reference maximum only when it would grow by more than the threshold
+                            const bool need = mx > m_ref + A_RESCALE_THRESHOLD || (m_ref == -INFINITY && mx > -INFINITY);
+                            if (__any_sync(0xffffffffu, need)) {
+                                float alpha = 1.0f;
+                                if (need) {
+                                    alpha = (m_ref == -INFINITY) ? 0.0f : fast_exp2(m_ref - mx);
+                                    m_ref = mx;
+                                    l_sum *= alpha;
                                 }
-                                tmem_st32(t_lane + A_COL_O + ob * A_D, o0);
-                                tmem_st32(t_lane + A_COL_O + ob * A_D + 32, o1);
-                                tc_wait_st();
+                                if (j > 0) {
+                                    const int pb = static_cast<int>((g - 1) & 1);
+                                    mbar_wait(&bars[AB_PV_DONE + pb], static_cast<uint32_t>(((g - 1) >> 1) & 1), wctx, AB_PV_DONE + pb);
+                                    tc_fence_after();
+                                    uint32_t o0[32], o1[32];
+                                    tmem_ld32(t_lane + A_COL_O + ob * A_D, o0);
+                                    tmem_ld32(t_lane + A_COL_O + ob * A_D + 32, o1);
+                                    tc_wait_ld();
+#pragma unroll
+                                    for (int i = 0; i < 32; ++i) {
+                                        o0[i] = __float_as_uint(__uint_as_float(o0[i]) * alpha);
+                                        o1[i] = __float_as_uint(__uint_as_float(o1[i]) * alpha);
+                                    }
+                                    tmem_st32(t_lane + A_COL_O + ob * A_D, o0);
+                                    tmem_st32(t_lane + A_COL_O + ob * A_D + 32, o1);
+                                    tc_wait_st();
+                                }
                             }
+                            l_sum += exp_tile((m_ref == -INFINITY) ? 0.0f : -m_ref);
                         }
-                        const float neg_m = (m_ref == -INFINITY) ? 0.0f : -m_ref;
-                        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-#pragma unroll
-                        for (int i = 0; i < 16; i += 2) {
-                            const float a0 = fast_exp2(fmaf(__uint_as_float(r0[2 * i]), scale, neg_m));
-                            const float a1 = fast_exp2(fmaf(__uint_as_float(r0[2 * i + 1]), scale, neg_m));
-                            const float a2 = fast_exp2(fmaf(__uint_as_float(r0[2 * i + 2]), scale, neg_m));
-                            const float a3 = fast_exp2(fmaf(__uint_as_float(r0[2 * i + 3]), scale, neg_m));
-                            s0 += a0; s1 += a1; s2 += a2; s3 += a3;
-                            r0[i] = pack_half2(a0, a1);
-                            r0[i + 1] = pack_half2(a2, a3);
-                        }
-#pragma unroll
-                        for (int i = 0; i < 16; i += 2) {
-                            const float a0 = fast_exp2(fmaf(__uint_as_float(r1[2 * i]), scale, neg_m));
-                            const float a1 = fast_exp2(fmaf(__uint_as_float(r1[2 * i + 1]), scale, neg_m));
-                            const float a2 = fast_exp2(fmaf(__uint_as_float(r1[2 * i + 2]), scale, neg_m));
-                            const float a3 = fast_exp2(fmaf(__uint_as_float(r1[2 * i + 3]), scale, neg_m));
-                            s0 += a0; s1 += a1; s2 += a2; s3 += a3;
-                            r0[16 + i] = pack_half2(a0, a1);
-                            r0[16 + i + 1] = pack_half2(a2, a3);
-                        }
-                        l_sum += (s0 + s1) + (s2 + s3);
                     }
                     // P overlays the first 32 columns of the S buffer it was computed from; the QK^T that next writes this
                     // buffer is issued after the PV product that reads P and the tensor core executes them in that order
@@ -537,7 +598,9 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 // ---------------------------------------------------------- item epilogue: O / l -> fp16 -> global
                 {
                     const int pb = static_cast<int>((g - 1) & 1);
+                    if (threadIdx.x == 0) TRACE(0, 128 + it);
                     mbar_wait(&bars[AB_PV_DONE + pb], static_cast<uint32_t>(((g - 1) >> 1) & 1), wctx, AB_PV_DONE + pb);
+                    if (threadIdx.x == 0) TRACE(1, 128 + it);
                     tc_fence_after();
                     uint32_t o0[32], o1[32];
                     tmem_ld32(t_lane + A_COL_O + ob * A_D, o0);
@@ -546,22 +609,25 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bars[AB_O_FREE + ob]);
-                    if (row < p.seq_len) {
+                    if (threadIdx.x == 0) TRACE(2, 128 + it);
+                    {
                         const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.0f;
+                        uint4 u[8];
 #pragma unroll
                         for (int c = 0; c < 8; ++c) {
                             const uint32_t* src = (c < 4) ? &o0[c * 8] : &o1[(c - 4) * 8];
-                            uint4 u;
-                            u.x = pack_half2(__uint_as_float(src[0]) * inv, __uint_as_float(src[1]) * inv);
-                            u.y = pack_half2(__uint_as_float(src[2]) * inv, __uint_as_float(src[3]) * inv);
-                            u.z = pack_half2(__uint_as_float(src[4]) * inv, __uint_as_float(src[5]) * inv);
-                            u.w = pack_half2(__uint_as_float(src[6]) * inv, __uint_as_float(src[7]) * inv);
-                            *reinterpret_cast<uint4*>(dst + 8 * c) = u;
+                            u[c].x = pack_half2(__uint_as_float(src[0]) * inv, __uint_as_float(src[1]) * inv);
+                            u[c].y = pack_half2(__uint_as_float(src[2]) * inv, __uint_as_float(src[3]) * inv);
+                            u[c].z = pack_half2(__uint_as_float(src[4]) * inv, __uint_as_float(src[5]) * inv);
+                            u[c].w = pack_half2(__uint_as_float(src[6]) * inv, __uint_as_float(src[7]) * inv);
                         }
+                        store_rows(u, cur_item);
                     }
+                    if (threadIdx.x == 0) TRACE(3, 128 + it);
                 }
                 ++it;
             }
+            if (lane == 0) tma_store_wait_all();             // every output store of this warp has been performed
         }
     }
     tc_fence_before();
@@ -572,7 +638,7 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     }
 }
 
-constexpr size_t A_SMEM_BYTES = 1024 + 2 * A_Q_BYTES + static_cast<size_t>(A_STAGES) * A_STAGE_BYTES + AB_COUNT * 8 + 16;
+constexpr size_t A_SMEM_BYTES = 1024 + 2 * A_Q_BYTES + static_cast<size_t>(A_STAGES) * A_STAGE_BYTES + 4 * A_OSTAGE_BYTES + AB_COUNT * 8 + 16;
 
 // Sorts the three outer dimensions (row, head, batch) by stride so that the tensor map's strides ascend;
 // returns the coordinate slot of each logical dimension.
@@ -685,8 +751,6 @@ extern "C" int stof_block_attn(const void* q, const void* k, const void* v, void
             STOF_REQUIRE(all[t][i] > 0 && all[t][i] % 8 == 0, "block_attn: strides must be positive multiples of 8 elements");
     }
     AttnParams p;
-    p.out = static_cast<__half*>(out);
-    p.o_stride_b = out_strides[0]; p.o_stride_h = out_strides[1]; p.o_stride_s = out_strides[2];
     p.part_row_ptr = part_row_ptr;
     p.part_block_mask = static_cast<const __half*>(part_block_mask);
     p.plan = static_cast<const unsigned char*>(plan);
@@ -710,7 +774,8 @@ extern "C" int stof_block_attn(const void* q, const void* k, const void* v, void
         g_trace_ptr = trace_buf;
     }
 #endif
-    CUtensorMap mq, mk, mv;
+    CUtensorMap mq, mk, mv, mo;
+    if (int rc = make_qkv_map(&mo, out, batch, heads, seq_len, out_strides, 32, &p.slot_s[3], &p.slot_h[3], &p.slot_b[3])) return rc;
     if (int rc = make_qkv_map(&mq, q, batch, heads, seq_len, q_strides, A_TQ, &p.slot_s[0], &p.slot_h[0], &p.slot_b[0])) return rc;
     if (int rc = make_qkv_map(&mk, k, batch, heads, seq_len, k_strides, A_TKV, &p.slot_s[1], &p.slot_h[1], &p.slot_b[1])) return rc;
     if (int rc = make_qkv_map(&mv, v, batch, heads, seq_len, v_strides, A_TKV, &p.slot_s[2], &p.slot_h[2], &p.slot_b[2])) return rc;
@@ -724,7 +789,7 @@ extern "C" int stof_block_attn(const void* q, const void* k, const void* v, void
     }
     long long grid = static_cast<long long>(A_CTAS_PER_SM) * sm_count();
     if (grid > items) grid = items;
-    block_attn_kernel<<<static_cast<unsigned>(grid), A_THREADS, A_SMEM_BYTES, stream>>>(mq, mk, mv, p);
+    block_attn_kernel<<<static_cast<unsigned>(grid), A_THREADS, A_SMEM_BYTES, stream>>>(mq, mk, mv, mo, p);
     STOF_CUDA(cudaGetLastError());
     return STOF_OK;
 }

@@ -51,14 +51,17 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
+// A waiting thread is suspended by the hardware until the phase completes or the hint (in ns) runs out, so
+// that polling threads do not take issue slots from the warps that do the arithmetic.
+constexpr uint32_t MBAR_SUSPEND_HINT_NS = 100000u;
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred P;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, P;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(MBAR_SUSPEND_HINT_NS)
         : "memory");
     return ok != 0;
 }
@@ -78,7 +81,7 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, const 
     const long long t0 = clock64();
     int spins = 0;
     while (!mbar_try_wait(bar, parity)) {
-        if ((++spins & 63) == 0) {
+        if ((++spins & 3) == 0) {
             if (*ctx.abort_smem) return;
             if (clock64() - t0 > WAIT_BUDGET_CYCLES) {
                 *ctx.abort_smem = 1;
@@ -107,6 +110,20 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m
         ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
 }
+
+// TMA tile store shared -> global (bulk async-group completion).  The writer makes its generic-proxy
+// shared-memory writes visible with fence_proxy_async_smem() before issuing the store.
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, const void* smem_src, int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+        ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// waits until the shared-memory source of every committed store group of this thread has been read
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// waits until every committed store group of this thread has completed (writes performed)
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // ---------------------------------------------------------------------------------
 // Tensor memory + tcgen05
@@ -205,10 +222,60 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// Packed fp32 pairs in one 64-bit register (add / sub / fma on both halves in one instruction).
+__device__ __forceinline__ uint64_t pk2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void upk2(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+// 2^x for a pair on the FMA pipe (no MUFU): round-to-nearest split x = n + f with f in [-0.5, 0.5] by the
+// 1.5 * 2^23 magic add, degree-3 minimax polynomial for 2^f (max relative error 7.5e-5, far below the
+// 4.9e-4 quantisation of the fp16 value it feeds), exponent inserted with an integer shift-add.
+// Inputs below -126 are clamped (the result is then ~1e-38 instead of 0).
+__device__ __forceinline__ void exp2_poly_pair(uint64_t x2, float& e0, float& e1) {
+    float x0, x1;
+    upk2(x2, x0, x1);
+    x0 = fmaxf(x0, -126.0f);
+    x1 = fmaxf(x1, -126.0f);
+    const uint64_t xc = pk2(x0, x1);
+    const uint64_t magic = pk2(12582912.0f, 12582912.0f);
+    const uint64_t xf = add2(xc, magic);
+    const uint64_t fr = sub2(xc, sub2(xf, magic));
+    uint64_t p = fma2(pk2(0.0551716685295105f, 0.0551716685295105f), fr, pk2(0.2426111251115799f, 0.2426111251115799f));
+    p = fma2(p, fr, pk2(0.6932609677314758f, 0.6932609677314758f));
+    p = fma2(p, fr, pk2(0.9999280571937561f, 0.9999280571937561f));
+    float p0, p1, f0, f1;
+    upk2(p, p0, p1);
+    upk2(xf, f0, f1);
+    // bits(p) + (n << 23) as one integer multiply-add (FMA pipe) per element
+    int i0, i1;
+    asm("mad.lo.s32 %0, %1, 8388608, %2;" : "=r"(i0) : "r"(__float_as_int(f0)), "r"(__float_as_int(p0)));
+    asm("mad.lo.s32 %0, %1, 8388608, %2;" : "=r"(i1) : "r"(__float_as_int(f1)), "r"(__float_as_int(p1)));
+    e0 = __int_as_float(i0);
+    e1 = __int_as_float(i1);
 }
 
 }  // namespace stof

@@ -5,7 +5,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-_LIB_PATH = os.path.join(_HERE, "libstof_b200.so")
+# STOF_B200_LIBRARY selects another build of the same library (for instance a debug build)
+_LIB_PATH = os.environ.get("STOF_B200_LIBRARY") or os.path.join(_HERE, "libstof_b200.so")
 
 STOF_DTYPE_F16, STOF_DTYPE_F32 = 0, 1
 EPI_BIAS, EPI_BIAS_GELU_ERF, EPI_BIAS_GELU_TANH, EPI_BIAS_RESIDUAL = 0, 1, 2, 3
