@@ -62,6 +62,35 @@ int stof_mask_fill(const void* mask, int mask_dtype, int seq_len, int block_m, i
                    void* part_block_mask, /* fp16 (n_part, block_m, block_n); may be NULL when n_part == 0 */
                    const void* workspace, size_t workspace_bytes, void* stream);
 
+/* Mask compaction for callers that must not allocate.
+ * No counterpart in the reference: its get_sparse_storage builds Python lists and allocates freely.
+ *
+ * Some hosts of this library cannot call cudaMalloc at the point where they need the block index: code
+ * that runs between a framework's allocator hooks, a plugin callback that is only handed its inputs and
+ * outputs, a latency-critical serving loop that has frozen its memory pool.  For them this single call
+ * does both phases of the compaction with the scratch (one class byte per tile plus a 16-byte header)
+ * in an array that is part of the library's device image instead of a workspace argument.  It calls no
+ * cudaMalloc / cudaFree and no allocating library routine; the caller passes every input and output.
+ *
+ * Limits and rules:
+ *  - (S / block_m) * (S / block_n) must not exceed 1,048,576 tiles (1 MiB of scratch; STOF_E_LIMIT
+ *    otherwise -- fall back to stof_mask_classify / stof_mask_fill with your own workspace).  Each GPU
+ *    that loads the library keeps that 1 MiB + 16 bytes resident until the process exits.
+ *  - The outputs are sized by the caller before the counts are known: the three column-index arrays hold
+ *    `col_capacity` entries each and `part_block_mask` holds `part_capacity` tiles; entries beyond a
+ *    capacity are dropped, and `counts` ({n_full, n_part, n_load, nnz_elements}, device) tells the caller
+ *    afterwards whether anything was.  Capacities of (S/block_m)*(S/block_n) never drop anything.
+ *  - The first call on a device looks up the array's device address (one runtime query, cached); make that
+ *    first call outside any stream capture.
+ *  - All calls share the one array and it keeps the previous call's bytes.  The call clears what has to
+ *    start at zero itself, but two calls whose kernels overlap on the GPU (different streams, or several
+ *    host threads) race on it: serialise them. */
+int stof_mask_compact_static(const void* mask, int mask_dtype, int batch, int seq_len, int block_m, int block_n,
+                             int* full_row_ptr, int* part_row_ptr, int* load_row_ptr,
+                             int* full_col_idx, int* part_col_idx, int* load_col_idx, long long col_capacity,
+                             void* part_block_mask, long long part_capacity,
+                             long long* counts, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Block-masked multi-head attention, fp16 in / fp16 out, fp32 accumulation, head_dim 64.
  * Replaces: launch_block_attn_mask(...), src/ops/src/block_attn_mask_cuda.cu:6026-6316, as bound by

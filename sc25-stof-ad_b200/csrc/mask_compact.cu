@@ -16,6 +16,8 @@
 
 #include <cuda_fp16.h>
 
+#include <mutex>
+
 namespace stof {
 namespace {
 
@@ -247,6 +249,100 @@ fill_kernel(const void* __restrict__ mask, int seq_len, int bm, int bn, const un
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Scratch for stof_mask_compact_static: lives in the module's device image instead of a caller
+// allocation.  Every GPU that loads the library holds these bytes until the process exits.
+// ---------------------------------------------------------------------------------------------
+constexpr int STATIC_MAX_TILES = 1 << 20;           // block rows x block columns the static scratch can classify
+static __device__ __align__(256) unsigned char g_static_scratch[WS_HEADER + STATIC_MAX_TILES];
+
+// Same ranking and gather as fill_kernel, but every write is checked against the capacity of the caller's
+// buffers (the caller sized them without knowing the counts): entries that do not fit are dropped.
+template <bool F32>
+__global__ void __launch_bounds__(FILL_THREADS)
+fill_bounded_kernel(const void* __restrict__ mask, int seq_len, int bm, int bn, const unsigned char* __restrict__ cls,
+                    const int* __restrict__ full_row_ptr, const int* __restrict__ part_row_ptr, const int* __restrict__ load_row_ptr,
+                    int* full_col_idx, int* part_col_idx, int* load_col_idx, long long col_capacity, __half* part_block_mask,
+                    long long part_capacity) {
+    extern __shared__ int s_part_cols[];
+    const int nbn = seq_len / bn;
+    const int brow = blockIdx.x, share = blockIdx.y, shares = gridDim.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int f0 = full_row_ptr[brow], p0 = part_row_ptr[brow], l0 = load_row_ptr[brow];
+    const int n_part = part_row_ptr[brow + 1] - p0;
+    if (warp == 0) {
+        int nf = 0, np = 0;
+        for (int c0 = 0; c0 < nbn; c0 += 32) {
+            const int c = c0 + lane;
+            const int k = c < nbn ? cls[static_cast<size_t>(brow) * nbn + c] : CLS_EMPTY;
+            const unsigned bf = __ballot_sync(0xffffffffu, k == CLS_FULL);
+            const unsigned bp = __ballot_sync(0xffffffffu, k == CLS_PART);
+            const unsigned lt = (1u << lane) - 1u;
+            const int rf = nf + __popc(bf & lt), rp = np + __popc(bp & lt);
+            if (k == CLS_FULL) {
+                if (share == 0) {
+                    if (f0 + rf < col_capacity) full_col_idx[f0 + rf] = c;
+                    if (l0 + rf + rp < col_capacity) load_col_idx[l0 + rf + rp] = c;
+                }
+            } else if (k == CLS_PART) {
+                s_part_cols[rp] = c;
+                if (share == 0) {
+                    if (p0 + rp < col_capacity) part_col_idx[p0 + rp] = c;
+                    if (l0 + rf + rp < col_capacity) load_col_idx[l0 + rf + rp] = c;
+                }
+            }
+            nf += __popc(bf);
+            np += __popc(bp);
+        }
+    }
+    __syncthreads();
+    if (n_part == 0 || part_block_mask == nullptr) return;
+    const int chunks_per_tile_row = bn / 8;
+    const int chunks_per_tile = bm * chunks_per_tile_row;
+    const __half one = __float2half(1.0f), neg = __float2half(-10000.0f);
+    for (int p = share; p < n_part; p += shares) {
+        if (p0 + p >= part_capacity) break;
+        const int c = s_part_cols[p];
+        __half* dst = part_block_mask + static_cast<size_t>(p0 + p) * bm * bn;
+        for (int idx = threadIdx.x; idx < chunks_per_tile; idx += blockDim.x) {
+            const int r = idx / chunks_per_tile_row, cc = idx - r * chunks_per_tile_row;
+            const size_t src = (static_cast<size_t>(brow) * bm + r) * seq_len + static_cast<size_t>(c) * bn + cc * 8;
+            __half h[8];
+            if (F32) {
+                const float4 a = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(mask) + src));
+                const float4 b = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(mask) + src + 4));
+                h[0] = __float2half_rn(a.x); h[1] = __float2half_rn(a.y); h[2] = __float2half_rn(a.z); h[3] = __float2half_rn(a.w);
+                h[4] = __float2half_rn(b.x); h[5] = __float2half_rn(b.y); h[6] = __float2half_rn(b.z); h[7] = __float2half_rn(b.w);
+            } else {
+                *reinterpret_cast<uint4*>(h) = __ldg(reinterpret_cast<const uint4*>(static_cast<const __half*>(mask) + src));
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) h[i] = __hmul(neg, __hsub(one, h[i]));
+            *reinterpret_cast<uint4*>(dst + static_cast<size_t>(r) * bn + cc * 8) = *reinterpret_cast<uint4*>(h);
+        }
+    }
+}
+
+// Device address of g_static_scratch on the current device.  In host code the array's name is only a
+// host-side handle, never a pointer a kernel may use, so the address is asked from the runtime once per
+// device (with that device current) and cached.
+int static_scratch_address(unsigned char** out) {
+    static std::mutex mu;
+    static unsigned char* addr[64] = {};
+    int dev = 0;
+    STOF_CUDA(cudaGetDevice(&dev));
+    STOF_REQUIRE(dev >= 0 && dev < 64, "mask_compact_static: device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (addr[dev] == nullptr) {
+        void* p = nullptr;
+        STOF_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+        STOF_REQUIRE(p != nullptr, "mask_compact_static: the runtime returned no address for the scratch array");
+        addr[dev] = static_cast<unsigned char*>(p);
+    }
+    *out = addr[dev];
+    return STOF_OK;
+}
+
 int check_geometry(int seq_len, int bm, int bn) {
     STOF_REQUIRE(seq_len > 0 && bm > 0 && bn > 0, "mask compaction: seq_len/block sizes must be positive");
     STOF_REQUIRE(seq_len % bm == 0 && seq_len % bn == 0, "mask compaction: seq_len %d is not a multiple of block_m %d and block_n %d",
@@ -333,6 +429,70 @@ extern "C" int stof_mask_fill(const void* mask, int mask_dtype, int seq_len, int
     else
         fill_kernel<false><<<grid, FILL_THREADS, smem, stream>>>(mask, seq_len, block_m, block_n, cls, full_row_ptr, part_row_ptr, load_row_ptr,
                                                                  full_col_idx, part_col_idx, load_col_idx, static_cast<__half*>(part_block_mask));
+    STOF_CUDA(cudaGetLastError());
+    return STOF_OK;
+}
+
+// One call, nothing allocated: classify + fill with the scratch in the library's own device image (see the header).
+extern "C" int stof_mask_compact_static(const void* mask, int mask_dtype, int batch, int seq_len, int block_m, int block_n,
+                                        int* full_row_ptr, int* part_row_ptr, int* load_row_ptr, int* full_col_idx, int* part_col_idx,
+                                        int* load_col_idx, long long col_capacity, void* part_block_mask, long long part_capacity,
+                                        long long* counts, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (int rc = check_geometry(seq_len, block_m, block_n)) return rc;
+    STOF_REQUIRE(mask && full_row_ptr && part_row_ptr && load_row_ptr && full_col_idx && part_col_idx && load_col_idx && counts,
+                 "mask_compact_static: null pointer");
+    STOF_REQUIRE(mask_dtype == STOF_DTYPE_F16 || mask_dtype == STOF_DTYPE_F32, "mask_compact_static: mask_dtype must be f16 or f32");
+    STOF_REQUIRE(batch >= 1 && batch <= 65535, "mask_compact_static: batch %d out of range", batch);
+    STOF_REQUIRE(col_capacity >= 0 && part_capacity >= 0, "mask_compact_static: negative capacity");
+    STOF_REQUIRE(aligned16(mask) && (part_block_mask == nullptr || aligned16(part_block_mask)), "mask_compact_static: 16-byte alignment required");
+    const int nbm = seq_len / block_m, nbn = seq_len / block_n;
+    STOF_REQUIRE(nbm <= 65535, "mask_compact_static: more than 65535 block rows");
+    if (static_cast<long long>(nbm) * nbn > STATIC_MAX_TILES) {
+        set_error("mask_compact_static: %d x %d blocks exceed the %d tiles the built-in scratch holds; use stof_mask_classify / stof_mask_fill "
+                  "with a workspace of your own", nbm, nbn, STATIC_MAX_TILES);
+        return STOF_E_LIMIT;
+    }
+    unsigned char* scratch = nullptr;
+    if (int rc = static_scratch_address(&scratch)) return rc;
+    Workspace* ws = reinterpret_cast<Workspace*>(scratch);
+    unsigned char* cls = scratch + WS_HEADER;
+
+    int unit = block_n;
+    while (unit < 256 && unit < seq_len) unit += block_n;
+    const int units = (seq_len + unit - 1) / unit;
+    int want = (4 * sm_count() + nbm * batch - 1) / (nbm * batch);
+    if (want < 1) want = 1;
+    if (want > units) want = units;
+    const int units_per_stripe = (units + want - 1) / want;
+    const int stripe_cols = units_per_stripe * unit;
+    const int stripes = (seq_len + stripe_cols - 1) / stripe_cols;
+
+    // the array keeps what the previous call left: the ticket and the totals must start at zero
+    STOF_CUDA(cudaMemsetAsync(ws, 0, WS_HEADER, stream));
+    STOF_CUDA(cudaMemsetAsync(counts, 0, 4 * sizeof(long long), stream));
+    dim3 grid(stripes, nbm, batch);
+    if (mask_dtype == STOF_DTYPE_F32)
+        classify_kernel<true><<<grid, CLASSIFY_THREADS, 0, stream>>>(mask, seq_len, block_m, block_n, stripe_cols, full_row_ptr, part_row_ptr,
+                                                                      load_row_ptr, reinterpret_cast<unsigned long long*>(counts), ws, cls);
+    else
+        classify_kernel<false><<<grid, CLASSIFY_THREADS, 0, stream>>>(mask, seq_len, block_m, block_n, stripe_cols, full_row_ptr, part_row_ptr,
+                                                                       load_row_ptr, reinterpret_cast<unsigned long long*>(counts), ws, cls);
+    STOF_CUDA(cudaGetLastError());
+    int shares = (4 * sm_count() + nbm - 1) / nbm;
+    if (shares < 1) shares = 1;
+    if (shares > 8) shares = 8;
+    if (part_block_mask == nullptr) shares = 1;
+    const size_t smem = static_cast<size_t>(nbn) * sizeof(int);
+    dim3 fgrid(nbm, shares);
+    if (mask_dtype == STOF_DTYPE_F32)
+        fill_bounded_kernel<true><<<fgrid, FILL_THREADS, smem, stream>>>(mask, seq_len, block_m, block_n, cls, full_row_ptr, part_row_ptr, load_row_ptr,
+                                                                         full_col_idx, part_col_idx, load_col_idx, col_capacity,
+                                                                         static_cast<__half*>(part_block_mask), part_capacity);
+    else
+        fill_bounded_kernel<false><<<fgrid, FILL_THREADS, smem, stream>>>(mask, seq_len, block_m, block_n, cls, full_row_ptr, part_row_ptr, load_row_ptr,
+                                                                          full_col_idx, part_col_idx, load_col_idx, col_capacity,
+                                                                          static_cast<__half*>(part_block_mask), part_capacity);
     STOF_CUDA(cudaGetLastError());
     return STOF_OK;
 }

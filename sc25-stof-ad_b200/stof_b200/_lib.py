@@ -11,7 +11,7 @@ _LIB_PATH = os.environ.get("STOF_B200_LIBRARY") or os.path.join(_HERE, "libstof_
 STOF_DTYPE_F16, STOF_DTYPE_F32 = 0, 1
 EPI_BIAS, EPI_BIAS_GELU_ERF, EPI_BIAS_GELU_TANH, EPI_BIAS_RESIDUAL = 0, 1, 2, 3
 
-EXPORTS = ("stof_version", "stof_last_error", "stof_mask_workspace_bytes", "stof_mask_classify", "stof_mask_fill",
+EXPORTS = ("stof_version", "stof_last_error", "stof_mask_workspace_bytes", "stof_mask_classify", "stof_mask_fill", "stof_mask_compact_static",
            "stof_block_attn_plan_bytes", "stof_block_attn_plan", "stof_block_attn", "stof_gemm_bias_act", "stof_bias_residual_layernorm")
 
 
@@ -46,6 +46,8 @@ def lib() -> ctypes.CDLL:
     L.stof_mask_classify.argtypes = [vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, sz, vp]
     L.stof_mask_fill.restype = i32
     L.stof_mask_fill.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp]
+    L.stof_mask_compact_static.restype = i32
+    L.stof_mask_compact_static.argtypes = [vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, i64, vp, i64, vp, vp]
     L.stof_block_attn_plan_bytes.restype = sz
     L.stof_block_attn_plan_bytes.argtypes = [i32, i32, i32]
     L.stof_block_attn_plan.restype = i32
