@@ -256,6 +256,8 @@ def run_attention(args, rank, world, local):
     mask_bytes = mask.numel() * 2
     comp_best = min(comp_ms)
     achieved = flops / (dev_ms / args.steps * 1e-3) / 1e12       # this rank's kernel
+    # DRAM read+write bytes of one launch from an ncu capture at batch 8 of the same mask (88.2 MB), scaled by batch
+    traffic = 88.196e6 * cfg.batch / 8 if cfg.mask == "bigbird" and cfg.seq_len == 2048 and cfg.heads == 12 else None
     line = {
         "metric": "masked-MHA effective TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -264,8 +266,9 @@ def run_attention(args, rank, world, local):
                    "mask": f"{cfg.mask} block {cfg.block}", "load_blocks": n_load, "flops_per_step_per_gpu": flops,
                    "l2": "256 MiB flush write between timed steps", "parallelism": f"independent batch shards x{world}"},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
-                     "traffic": None, "peak_source": peaks["source"] + " bf16 burst", "frac_of_sustained": achieved / peaks["tflops_sustained"],
-                     "kernel": "block_attn_kernel"},
+                     "traffic": traffic, "traffic_unit": "bytes per launch (ncu dram read+write, batch-8 capture scaled)",
+                     "algorithmic_bytes": 4 * q.numel() * 2, "peak_source": peaks["source"] + " bf16 burst",
+                     "frac_of_sustained": achieved / peaks["tflops_sustained"], "kernel": "block_attn_kernel"},
         "cpu_baseline": {"value": cpu_val, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port", "sample": cpu_desc,
                          "seconds": cpu_s},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
