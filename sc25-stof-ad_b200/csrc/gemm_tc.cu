@@ -5,8 +5,9 @@
 //               i.e. N-major as the weights lie in memory) per stage, 4 stages of 48 KB
 //   warp 9      MMA issuer: 4 tcgen05.mma (128 x 256 x 16) per stage into one of two 256-column fp32
 //               accumulators in tensor memory; tcgen05.commit releases the stage / publishes the tile
-//   warps 0-7   epilogue: tcgen05.ld 32 columns at a time, + bias, optional GELU (erf or tanh form) or
-//               + residual, fp16 pack, 128-bit stores; runs under the next tile's main loop
+//   warps 0-7   epilogue: tcgen05.ld 64 columns at a time, + bias, optional GELU (erf or tanh form, evaluated on
+//               packed fp32 pairs) or + residual (prefetched into registers before the accumulator is ready),
+//               fp16 pack into a swizzled shared-memory slab, TMA store; runs under the next tile's main loop
 // Weights are consumed in their (K, N) row-major layout through an MN-major shared-memory
 // descriptor, so no transposed copy is ever made.
 #include "stof_host.h"
@@ -23,24 +24,57 @@ constexpr int G_STAGE_BYTES = G_A_BYTES + G_B_BYTES;  // 48 KB
 constexpr int G_EPI_WARPS = 8;
 constexpr int G_THREADS = (G_EPI_WARPS + 2) * 32;
 constexpr int G_TMEM_COLS = 512;
-constexpr size_t G_SMEM = 1024 + static_cast<size_t>(G_STAGES) * G_STAGE_BYTES + 256;
+constexpr int G_SLAB_BYTES = 32 * 64 * 2;                // per epilogue warp: 32 rows x 64 columns of fp16 (TMA store source)
+constexpr size_t G_SMEM = 1024 + static_cast<size_t>(G_STAGES) * G_STAGE_BYTES + G_EPI_WARPS * G_SLAB_BYTES + 256;
 
 enum { BAR_FULL = 0, BAR_EMPTY = G_STAGES, BAR_TFULL = 2 * G_STAGES, BAR_TEMPTY = 2 * G_STAGES + 2, BAR_COUNT = 2 * G_STAGES + 4 };
 
-__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
-__device__ __forceinline__ float gelu_tanh(float x) {
-    const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-    return 0.5f * x * (1.0f + tanhf(u));
+// erf-form GELU on a packed pair: 0.5 x (1 + erf(x / sqrt 2)) with erf(z) = sign(z) (1 - 1 / p(|z|)^16),
+// p a degree-6 polynomial (Abramowitz & Stegun 7.1.28, |error| <= 3e-7): six packed FMAs, four packed squarings and one
+// reciprocal per element instead of the ~30 instructions of erff.
+__device__ __forceinline__ uint64_t gelu_erf2(uint64_t x2) {
+    float x0, x1;
+    upk2(x2, x0, x1);
+    const uint64_t z = pk2(fabsf(x0) * 0.70710678118654752f, fabsf(x1) * 0.70710678118654752f);
+    uint64_t p = fma2(pk2(0.0000430638f, 0.0000430638f), z, pk2(0.0002765672f, 0.0002765672f));
+    p = fma2(p, z, pk2(0.0001520143f, 0.0001520143f));
+    p = fma2(p, z, pk2(0.0092705272f, 0.0092705272f));
+    p = fma2(p, z, pk2(0.0422820123f, 0.0422820123f));
+    p = fma2(p, z, pk2(0.0705230784f, 0.0705230784f));
+    p = fma2(p, z, pk2(1.0f, 1.0f));
+    p = mul2(p, p);
+    p = mul2(p, p);
+    p = mul2(p, p);
+    p = mul2(p, p);
+    float p0, p1;
+    upk2(p, p0, p1);
+    const float e0 = copysignf(1.0f - __fdividef(1.0f, p0), x0);      // p^16 = inf for large |x| gives erf = +-1
+    const float e1 = copysignf(1.0f - __fdividef(1.0f, p1), x1);
+    const uint64_t hx = mul2(x2, pk2(0.5f, 0.5f));
+    return fma2(hx, pk2(e0, e1), hx);
+}
+// tanh-form GELU: 0.5 x (1 + tanh(u)) = x * sigmoid(2u), u = 0.79788456 (x + 0.044715 x^3)
+__device__ __forceinline__ uint64_t gelu_tanh2(uint64_t x2) {
+    const uint64_t xx = mul2(x2, x2);
+    const uint64_t inner = fma2(xx, pk2(0.044715f * 0.7978845608028654f, 0.044715f * 0.7978845608028654f),
+                                pk2(0.7978845608028654f, 0.7978845608028654f));
+    float u0, u1, x0, x1;
+    upk2(mul2(inner, x2), u0, u1);
+    upk2(x2, x0, x1);
+    // sigmoid(2u) = 1 / (1 + 2^(-2u log2 e))
+    const float s0 = __fdividef(1.0f, 1.0f + fast_exp2(-2.8853900817779268f * u0));
+    const float s1 = __fdividef(1.0f, 1.0f + fast_exp2(-2.8853900817779268f * u1));
+    return pk2(x0 * s0, x1 * s1);
 }
 
 template <int EPI>
 __global__ void __launch_bounds__(G_THREADS, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const __half* __restrict__ bias,
-            const __half* __restrict__ residual, long long ldr, __half* __restrict__ c, long long ldc, int m, int n, int k,
-            int* status) {
+gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_c,
+            const __half* __restrict__ bias, const __half* __restrict__ residual, long long ldr, int m, int n, int k, int* status) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + G_STAGES * G_STAGE_BYTES);
+    unsigned char* slabs = smem + G_STAGES * G_STAGE_BYTES;          // one 4 KB slab per epilogue warp, 1024-aligned
+    uint64_t* bars = reinterpret_cast<uint64_t*>(slabs + G_EPI_WARPS * G_SLAB_BYTES);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + BAR_COUNT);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -126,69 +160,94 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         } else {
             // ------------------------------------------------------------------ epilogue
             const int quarter = warp & 3, half_n = warp >> 2;
+            unsigned char* slab = slabs + warp * G_SLAB_BYTES;
             int local = 0;
             for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++local) {
                 const int acc = local & 1;
                 const uint32_t acc_ph = (local >> 1) & 1;
                 const int m0 = (t / tiles_n) * G_BM, n0 = (t % tiles_n) * G_BN;
+                const int row0 = m0 + quarter * 32;
+                const int row = row0 + lane;
+                const int colbase = n0 + half_n * (G_BN / 2);
+                // the residual does not depend on the accumulator: its loads are in flight while the tile's MMAs finish
+                uint4 res[2][8];
+                if (EPI == STOF_EPI_BIAS_RESIDUAL) {
+#pragma unroll
+                    for (int ch = 0; ch < 2; ++ch)
+#pragma unroll
+                        for (int g = 0; g < 8; ++g) {
+                            const int col = colbase + ch * 64 + g * 8;
+                            res[ch][g] = (row < m && col < n) ? __ldg(reinterpret_cast<const uint4*>(residual + static_cast<size_t>(row) * ldr + col))
+                                                              : make_uint4(0u, 0u, 0u, 0u);
+                        }
+                }
                 mbar_wait(&bars[BAR_TFULL + acc], acc_ph, wctx, BAR_TFULL + acc);
                 tc_fence_after();
-                const int row = m0 + quarter * 32 + lane;
                 const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * G_BN + half_n * (G_BN / 2);
-#pragma unroll 1
-                for (int ch = 0; ch < G_BN / 2 / 32; ++ch) {
-                    uint32_t r[32];
-                    tmem_ld32(t_row + ch * 32, r);
+#pragma unroll
+                for (int ch = 0; ch < 2; ++ch) {
+                    uint32_t r0[32], r1[32];
+                    tmem_ld32(t_row + ch * 64, r0);
+                    tmem_ld32(t_row + ch * 64 + 32, r1);
                     tc_wait_ld();
-                    const int col0 = n0 + half_n * (G_BN / 2) + ch * 32;
-                    if (row < m && col0 < n) {
+                    if (ch == 1) {
+                        // both chunks of this accumulator half are in registers: hand the accumulator back to the MMA warp
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&bars[BAR_TEMPTY + acc]);
+                    }
+                    const int col0 = colbase + ch * 64;
+                    if (col0 < n && row0 < m) {
+                        if (lane == 0) tma_store_wait_read();             // the slab's previous store has been read out
+                        __syncwarp();
 #pragma unroll
-                        for (int g = 0; g < 4; ++g) {
+                        for (int g = 0; g < 8; ++g) {                     // 8 columns = one 16-byte chunk of the output row
+                            const uint32_t* src = (g < 4) ? &r0[8 * g] : &r1[8 * (g - 4)];
                             const int col = col0 + 8 * g;
-                            if (col < n) {
-                                float v[8];
+                            uint64_t v[4];
 #pragma unroll
-                                for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[8 * g + j]);
-                                if (bias) {
-                                    const uint4 bu = __ldg(reinterpret_cast<const uint4*>(bias + col));
-                                    const __half2* bh = reinterpret_cast<const __half2*>(&bu);
+                            for (int j = 0; j < 4; ++j) v[j] = pk2(__uint_as_float(src[2 * j]), __uint_as_float(src[2 * j + 1]));
+                            if (bias != nullptr && col < n) {
+                                const uint4 bu = __ldg(reinterpret_cast<const uint4*>(bias + col));
+                                const __half2* bh = reinterpret_cast<const __half2*>(&bu);
 #pragma unroll
-                                    for (int j = 0; j < 4; ++j) {
-                                        const float2 f = __half22float2(bh[j]);
-                                        v[2 * j] += f.x;
-                                        v[2 * j + 1] += f.y;
-                                    }
+                                for (int j = 0; j < 4; ++j) {
+                                    const float2 f = __half22float2(bh[j]);
+                                    v[j] = add2(v[j], pk2(f.x, f.y));
                                 }
-                                if (EPI == STOF_EPI_BIAS_GELU_ERF) {
-#pragma unroll
-                                    for (int j = 0; j < 8; ++j) v[j] = gelu_erf(v[j]);
-                                } else if (EPI == STOF_EPI_BIAS_GELU_TANH) {
-#pragma unroll
-                                    for (int j = 0; j < 8; ++j) v[j] = gelu_tanh(v[j]);
-                                } else if (EPI == STOF_EPI_BIAS_RESIDUAL) {
-                                    const uint4 ru = __ldg(reinterpret_cast<const uint4*>(residual + static_cast<size_t>(row) * ldr + col));
-                                    const __half2* rh = reinterpret_cast<const __half2*>(&ru);
-#pragma unroll
-                                    for (int j = 0; j < 4; ++j) {
-                                        const float2 f = __half22float2(rh[j]);
-                                        v[2 * j] += f.x;
-                                        v[2 * j + 1] += f.y;
-                                    }
-                                }
-                                uint4 o;
-                                o.x = pack_half2(v[0], v[1]);
-                                o.y = pack_half2(v[2], v[3]);
-                                o.z = pack_half2(v[4], v[5]);
-                                o.w = pack_half2(v[6], v[7]);
-                                *reinterpret_cast<uint4*>(c + static_cast<size_t>(row) * ldc + col) = o;
                             }
+                            if (EPI == STOF_EPI_BIAS_GELU_ERF) {
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) v[j] = gelu_erf2(v[j]);
+                            } else if (EPI == STOF_EPI_BIAS_GELU_TANH) {
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) v[j] = gelu_tanh2(v[j]);
+                            } else if (EPI == STOF_EPI_BIAS_RESIDUAL) {
+                                const __half2* rh = reinterpret_cast<const __half2*>(&res[ch][g]);
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    const float2 f = __half22float2(rh[j]);
+                                    v[j] = add2(v[j], pk2(f.x, f.y));
+                                }
+                            }
+                            uint4 o;
+                            float lo, hi;
+                            upk2(v[0], lo, hi); o.x = pack_half2(lo, hi);
+                            upk2(v[1], lo, hi); o.y = pack_half2(lo, hi);
+                            upk2(v[2], lo, hi); o.z = pack_half2(lo, hi);
+                            upk2(v[3], lo, hi); o.w = pack_half2(lo, hi);
+                            *reinterpret_cast<uint4*>(slab + lane * 128 + ((g ^ (lane & 7)) << 4)) = o;
+                        }
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_store_2d(&map_c, slab, col0, row0);       // rows / columns beyond the matrix are clipped by the tensor map
+                            tma_store_commit();
                         }
                     }
                 }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bars[BAR_TEMPTY + acc]);
             }
+            if (lane == 0) tma_store_wait_all();
         }
     }
     tc_fence_before();
@@ -200,7 +259,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 }
 
 template <int EPI>
-int launch(const CUtensorMap& ma, const CUtensorMap& mw, const __half* bias, const __half* residual, long long ldr, __half* c, long long ldc,
+int launch(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mc, const __half* bias, const __half* residual, long long ldr,
            int m, int n, int k, int* status, cudaStream_t stream) {
     static bool configured[64] = {};
     int dev = 0;
@@ -212,7 +271,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, const __half* bias, con
     const int tiles = ((m + G_BM - 1) / G_BM) * ((n + G_BN - 1) / G_BN);
     int grid = sm_count();
     if (grid > tiles) grid = tiles;
-    gemm_kernel<EPI><<<grid, G_THREADS, G_SMEM, stream>>>(ma, mw, bias, residual, ldr, c, ldc, m, n, k, status);
+    gemm_kernel<EPI><<<grid, G_THREADS, G_SMEM, stream>>>(ma, mw, mc, bias, residual, ldr, m, n, k, status);
     STOF_CUDA(cudaGetLastError());
     return STOF_OK;
 }
@@ -250,12 +309,18 @@ extern "C" int stof_gemm_bias_act(const void* a, long long lda, const void* w, l
         const uint32_t box[2] = {64, G_BK};
         if (int rc = make_tensor_map_f16(&mw, w, 2, dims, strides, box)) return rc;
     }
+    CUtensorMap mc;
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(n), static_cast<uint64_t>(m)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(ldc) * 2};
+        const uint32_t box[2] = {64, 32};
+        if (int rc = make_tensor_map_f16(&mc, c, 2, dims, strides, box)) return rc;
+    }
     const __half *bp = static_cast<const __half*>(bias), *rp = static_cast<const __half*>(residual);
-    __half* cp = static_cast<__half*>(c);
     switch (epilogue) {
-        case STOF_EPI_BIAS: return launch<STOF_EPI_BIAS>(ma, mw, bp, rp, ldr, cp, ldc, m, n, k, status_dev, stream);
-        case STOF_EPI_BIAS_GELU_ERF: return launch<STOF_EPI_BIAS_GELU_ERF>(ma, mw, bp, rp, ldr, cp, ldc, m, n, k, status_dev, stream);
-        case STOF_EPI_BIAS_GELU_TANH: return launch<STOF_EPI_BIAS_GELU_TANH>(ma, mw, bp, rp, ldr, cp, ldc, m, n, k, status_dev, stream);
-        default: return launch<STOF_EPI_BIAS_RESIDUAL>(ma, mw, bp, rp, ldr, cp, ldc, m, n, k, status_dev, stream);
+        case STOF_EPI_BIAS: return launch<STOF_EPI_BIAS>(ma, mw, mc, bp, rp, ldr, m, n, k, status_dev, stream);
+        case STOF_EPI_BIAS_GELU_ERF: return launch<STOF_EPI_BIAS_GELU_ERF>(ma, mw, mc, bp, rp, ldr, m, n, k, status_dev, stream);
+        case STOF_EPI_BIAS_GELU_TANH: return launch<STOF_EPI_BIAS_GELU_TANH>(ma, mw, mc, bp, rp, ldr, m, n, k, status_dev, stream);
+        default: return launch<STOF_EPI_BIAS_RESIDUAL>(ma, mw, mc, bp, rp, ldr, m, n, k, status_dev, stream);
     }
 }
