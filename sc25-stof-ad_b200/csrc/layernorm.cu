@@ -1,11 +1,12 @@
 // y = LayerNorm(x + bias + residual) * gamma + beta over rows of fp16, fp32 statistics (HBM-bound).
 //
-// One warp per row.  The row is read once with 128-bit loads, held in registers as fp32, reduced
-// with warp shuffles (mean, then the centred sum of squares, biased variance as
-// src/triton_template/add_layernorm.py:33-55 and F.layer_norm do), and written once with 128-bit
-// stores.  Rows longer than 2048 elements are re-read from cache for the second and third sweep
+// One warp per row, persistent over rows.  A row is read once with 128-bit loads (the next row of the warp is
+// already in flight), held in registers as fp32, reduced with warp shuffles (mean, then the centred sum of
+// squares, biased variance as src/triton_template/add_layernorm.py:33-55 and F.layer_norm do), and written once
+// with 128-bit stores.  Rows longer than 2048 elements are re-read from cache for the second and third sweep
 // instead of being held in registers.
 #include "stof_host.h"
+#include "stof_ptx.cuh"
 
 #include <cuda_fp16.h>
 
@@ -13,6 +14,8 @@ namespace stof {
 namespace {
 
 constexpr int LN_WARPS = 8;
+constexpr int LN_BLOCKS_PER_SM = 4;
+constexpr int LN_STAGES = 3;
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -47,103 +50,163 @@ __device__ __forceinline__ void store8(__half* p, const float (&f)[8]) {
 }
 
 // NCHUNK: 16-byte chunks held per lane (hidden <= NCHUNK * 256); NCHUNK == 0 selects the re-reading variant.
+// Persistent: each warp walks rows warp, warp + W, ...  Rows (and residual rows) arrive through a per-warp ring of
+// LN_STAGES shared-memory buffers filled by 1-D bulk copies, so that two further rows per warp are always in flight and
+// the kernel keeps enough bytes outstanding to cover the HBM latency without spending registers on it.
 template <int NCHUNK>
 __global__ void __launch_bounds__(LN_WARPS * 32)
 layernorm_kernel(const __half* x, long long ldx, const __half* __restrict__ bias, const __half* __restrict__ residual,
                  long long ldr, const __half* __restrict__ gamma, const __half* __restrict__ beta, float eps, __half* y,
                  long long ldy, int rows, int hidden) {
-    const int lane = threadIdx.x & 31;
-    const int row = blockIdx.x * LN_WARPS + (threadIdx.x >> 5);
+    extern __shared__ __align__(128) unsigned char ln_smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int warps_total = gridDim.x * LN_WARPS;
+    int row = blockIdx.x * LN_WARPS + warp;
     if (row >= rows) return;
-    const __half* xr = x + static_cast<size_t>(row) * ldx;
-    const __half* rr = residual ? residual + static_cast<size_t>(row) * ldr : nullptr;
-    __half* yr = y + static_cast<size_t>(row) * ldy;
     const int nchunks = hidden >> 3;
     const float inv_n = 1.0f / static_cast<float>(hidden);
 
     if constexpr (NCHUNK > 0) {
-        float v[NCHUNK][8];
-        float sum = 0.f;
-#pragma unroll
-        for (int i = 0; i < NCHUNK; ++i) {
-            const int c = lane + 32 * i;
-            if (c < nchunks) {
-                load8(xr + 8 * c, v[i]);
-                if (bias) add8(bias + 8 * c, v[i]);
-                if (rr) add8(rr + 8 * c, v[i]);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) sum += v[i][j];
-            }
+        const uint32_t row_bytes = static_cast<uint32_t>(hidden) * 2u;
+        const uint32_t slot_bytes = residual ? 2u * row_bytes : row_bytes;
+        uint64_t* bars = reinterpret_cast<uint64_t*>(ln_smem) + warp * LN_STAGES;
+        unsigned char* ring = ln_smem + LN_WARPS * LN_STAGES * 8 + static_cast<size_t>(warp) * LN_STAGES * slot_bytes;
+        if (lane == 0) {
+            for (int s = 0; s < LN_STAGES; ++s) mbar_init(&bars[s], 1);
+            fence_mbar_init();
         }
-        const float mean = warp_sum(sum) * inv_n;
-        float sq = 0.f;
+        __syncwarp();
+        auto issue = [&](int r, int s) {                 // lane 0 only
+            unsigned char* dst = ring + static_cast<size_t>(s) * slot_bytes;
+            mbar_arrive_expect_tx(&bars[s], slot_bytes);
+            bulk_load_1d(dst, x + static_cast<size_t>(r) * ldx, row_bytes, &bars[s]);
+            if (residual) bulk_load_1d(dst + row_bytes, residual + static_cast<size_t>(r) * ldr, row_bytes, &bars[s]);
+        };
+        if (lane == 0) {
 #pragma unroll
-        for (int i = 0; i < NCHUNK; ++i) {
-            if (lane + 32 * i < nchunks) {
+            for (int s = 0; s < LN_STAGES - 1; ++s)
+                if (row + s * warps_total < rows) issue(row + s * warps_total, s);
+        }
+        auto unpack = [](const uint4& u, float (&f)[8]) {
+            const __half2* h = reinterpret_cast<const __half2*>(&u);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const float d = v[i][j] - mean;
-                    sq += d * d;
+            for (int i = 0; i < 4; ++i) {
+                const float2 t = __half22float2(h[i]);
+                f[2 * i] = t.x;
+                f[2 * i + 1] = t.y;
+            }
+        };
+        for (int it = 0; row < rows; row += warps_total, ++it) {
+            const int s = it % LN_STAGES;
+            const uint32_t parity = static_cast<uint32_t>((it / LN_STAGES) & 1);
+            // completes with the copy (no partner thread involved); bounded all the same: ~1.6 s of suspended polls
+            for (int spin = 0; !mbar_try_wait(&bars[s], parity) && spin < (1 << 14); ++spin) { }
+            const unsigned char* src = ring + static_cast<size_t>(s) * slot_bytes;
+            float v[NCHUNK][8];
+            float sum = 0.f;
+#pragma unroll
+            for (int i = 0; i < NCHUNK; ++i) {
+                const int c = lane + 32 * i;
+                if (c < nchunks) {
+                    unpack(*reinterpret_cast<const uint4*>(src + 16 * c), v[i]);
+                    float t[8];
+                    if (residual) {
+                        unpack(*reinterpret_cast<const uint4*>(src + row_bytes + 16 * c), t);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) v[i][j] += t[j];
+                    }
+                    if (bias) {
+                        unpack(__ldg(reinterpret_cast<const uint4*>(bias + 8 * c)), t);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) v[i][j] += t[j];
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) sum += v[i][j];
+                }
+            }
+            // this slot is read out: refill the slot that was consumed one row ago with the row LN_STAGES - 1 ahead
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                const int ahead = row + (LN_STAGES - 1) * warps_total;
+                if (ahead < rows) issue(ahead, (it + LN_STAGES - 1) % LN_STAGES);
+            }
+            const float mean = warp_sum(sum) * inv_n;
+            float sq = 0.f;
+#pragma unroll
+            for (int i = 0; i < NCHUNK; ++i) {
+                if (lane + 32 * i < nchunks) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float d = v[i][j] - mean;
+                        sq += d * d;
+                    }
+                }
+            }
+            const float rstd = 1.0f / sqrtf(warp_sum(sq) * inv_n + eps);
+            __half* yr = y + static_cast<size_t>(row) * ldy;
+#pragma unroll
+            for (int i = 0; i < NCHUNK; ++i) {
+                const int c = lane + 32 * i;
+                if (c < nchunks) {
+                    float g[8], b[8];
+                    if (gamma) unpack(__ldg(reinterpret_cast<const uint4*>(gamma + 8 * c)), g);
+                    if (beta) unpack(__ldg(reinterpret_cast<const uint4*>(beta + 8 * c)), b);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        float o = (v[i][j] - mean) * rstd;
+                        if (gamma) o *= g[j];
+                        if (beta) o += b[j];
+                        v[i][j] = o;
+                    }
+                    store8(yr + 8 * c, v[i]);
                 }
             }
         }
-        const float rstd = 1.0f / sqrtf(warp_sum(sq) * inv_n + eps);
+    } else {
+        for (; row < rows; row += warps_total) {
+            const __half* xr = x + static_cast<size_t>(row) * ldx;
+            const __half* rr = residual ? residual + static_cast<size_t>(row) * ldr : nullptr;
+            __half* yr = y + static_cast<size_t>(row) * ldy;
+            float sum = 0.f;
+            for (int c = lane; c < nchunks; c += 32) {
+                float t[8];
+                load8(xr + 8 * c, t);
+                if (bias) add8(bias + 8 * c, t);
+                if (rr) add8(rr + 8 * c, t);
 #pragma unroll
-        for (int i = 0; i < NCHUNK; ++i) {
-            const int c = lane + 32 * i;
-            if (c < nchunks) {
-                float g[8], b[8];
+                for (int j = 0; j < 8; ++j) sum += t[j];
+            }
+            const float mean = warp_sum(sum) * inv_n;
+            float sq = 0.f;
+            for (int c = lane; c < nchunks; c += 32) {
+                float t[8];
+                load8(xr + 8 * c, t);
+                if (bias) add8(bias + 8 * c, t);
+                if (rr) add8(rr + 8 * c, t);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float d = t[j] - mean;
+                    sq += d * d;
+                }
+            }
+            const float rstd = 1.0f / sqrtf(warp_sum(sq) * inv_n + eps);
+            for (int c = lane; c < nchunks; c += 32) {
+                float t[8], g[8], b[8];
+                load8(xr + 8 * c, t);
+                if (bias) add8(bias + 8 * c, t);
+                if (rr) add8(rr + 8 * c, t);
                 if (gamma) load8(gamma + 8 * c, g);
                 if (beta) load8(beta + 8 * c, b);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    float o = (v[i][j] - mean) * rstd;
+                    float o = (t[j] - mean) * rstd;
                     if (gamma) o *= g[j];
                     if (beta) o += b[j];
-                    v[i][j] = o;
+                    t[j] = o;
                 }
-                store8(yr + 8 * c, v[i]);
+                store8(yr + 8 * c, t);
             }
-        }
-    } else {
-        float sum = 0.f;
-        for (int c = lane; c < nchunks; c += 32) {
-            float t[8];
-            load8(xr + 8 * c, t);
-            if (bias) add8(bias + 8 * c, t);
-            if (rr) add8(rr + 8 * c, t);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) sum += t[j];
-        }
-        const float mean = warp_sum(sum) * inv_n;
-        float sq = 0.f;
-        for (int c = lane; c < nchunks; c += 32) {
-            float t[8];
-            load8(xr + 8 * c, t);
-            if (bias) add8(bias + 8 * c, t);
-            if (rr) add8(rr + 8 * c, t);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const float d = t[j] - mean;
-                sq += d * d;
-            }
-        }
-        const float rstd = 1.0f / sqrtf(warp_sum(sq) * inv_n + eps);
-        for (int c = lane; c < nchunks; c += 32) {
-            float t[8], g[8], b[8];
-            load8(xr + 8 * c, t);
-            if (bias) add8(bias + 8 * c, t);
-            if (rr) add8(rr + 8 * c, t);
-            if (gamma) load8(gamma + 8 * c, g);
-            if (beta) load8(beta + 8 * c, b);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                float o = (t[j] - mean) * rstd;
-                if (gamma) o *= g[j];
-                if (beta) o += b[j];
-                t[j] = o;
-            }
-            store8(yr + 8 * c, t);
         }
     }
 }
@@ -169,11 +232,21 @@ extern "C" int stof_bias_residual_layernorm(const void* x, long long ldx, const 
     STOF_REQUIRE(aligned16(x) && aligned16(y) && aligned16(bias) && aligned16(residual) && aligned16(gamma) && aligned16(beta),
                  "layernorm: pointers must be 16-byte aligned");
     if (rows == 0) return STOF_OK;
-    const dim3 grid((rows + LN_WARPS - 1) / LN_WARPS), block(LN_WARPS * 32);
+    // persistent grid: enough warps to keep the memory system busy, never more blocks than rows need
+    int blocks = (rows + LN_WARPS - 1) / LN_WARPS;
+    const int cap = sm_count() * LN_BLOCKS_PER_SM;
+    if (blocks > cap) blocks = cap;
+    const dim3 grid(blocks), block(LN_WARPS * 32);
     const __half *xp = static_cast<const __half*>(x), *bp = static_cast<const __half*>(bias), *rp = static_cast<const __half*>(residual),
                  *gp = static_cast<const __half*>(gamma), *tp = static_cast<const __half*>(beta);
     __half* yp = static_cast<__half*>(y);
-#define STOF_LN_LAUNCH(N) layernorm_kernel<N><<<grid, block, 0, stream>>>(xp, ldx, bp, rp, ldr, gp, tp, eps, yp, ldy, rows, hidden)
+    const size_t ring_smem = hidden <= 2048 ? static_cast<size_t>(LN_WARPS) * LN_STAGES * (8 + static_cast<size_t>(hidden) * 2 * (residual ? 2 : 1)) : 0;
+#define STOF_LN_LAUNCH(N)                                                                                                           \
+    do {                                                                                                                            \
+        if (ring_smem > 48 * 1024)                                                                                                  \
+            STOF_CUDA(cudaFuncSetAttribute(layernorm_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(ring_smem))); \
+        layernorm_kernel<N><<<grid, block, ring_smem, stream>>>(xp, ldx, bp, rp, ldr, gp, tp, eps, yp, ldy, rows, hidden);      \
+    } while (0)
     if (hidden <= 256) STOF_LN_LAUNCH(1);
     else if (hidden <= 512) STOF_LN_LAUNCH(2);
     else if (hidden <= 768) STOF_LN_LAUNCH(3);
