@@ -31,10 +31,7 @@ constexpr int A_KV_BYTES = A_TKV * A_D * 2;       // 8 KB each for K and V
 constexpr int A_STAGE_BYTES = 2 * A_KV_BYTES;
 constexpr int A_OSTAGE_BYTES = 32 * A_D * 2;     // 4 KB output staging per softmax warp (TMA store source)
 constexpr int A_THREADS = 192;
-#ifndef A_CTAS
-#define A_CTAS 2
-#endif
-constexpr int A_CTAS_PER_SM = A_CTAS;
+constexpr int A_CTAS_PER_SM = 2;
 constexpr int A_TMEM_COLS = 256;
 constexpr int A_COL_S = 0, A_COL_O = 128;         // S0 @0, S1 @64 (P overlays the first 32 columns of its S), O0 @128, O1 @192
 constexpr int A_MAX_TABLE_BYTES = 48 * 1024;
@@ -177,9 +174,6 @@ struct AttnParams {
     int slot_s[4], slot_h[4], slot_b[4];   // coordinate slot (1..3) of row / head / batch in the q, k, v, out tensor maps
     float scale_log2;
     int* status;
-#ifdef STOF_TRACE
-    long long* trace;
-#endif
 };
 
 __device__ __forceinline__ void tma_tile(void* dst, const CUtensorMap* map, uint64_t* bar, int row, int h, int b, int ss, int sh, int sb) {
@@ -222,12 +216,6 @@ __device__ __forceinline__ Item fetch_item(unsigned k, const AttnParams& p, cons
     it.head = static_cast<int>(bh - it.batch * p.heads);
     return it;
 }
-
-#ifdef STOF_TRACE
-#define TRACE(slot, step) do { if (blockIdx.x == 0 && (step) < 256) p.trace[(step) * 8 + (slot)] = clock64(); } while (0)
-#else
-#define TRACE(slot, step) do { } while (0)
-#endif
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float d;
@@ -369,9 +357,7 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                             mbar_wait(&bars[AB_O_FREE + qb], static_cast<uint32_t>(((it >> 1) & 1) ^ 1), wctx, AB_O_FREE + qb);
                         }
                         const int b = static_cast<int>(g & 1), s = static_cast<int>(g % A_STAGES);
-                        TRACE(5, g);
                         mbar_wait(&bars[AB_P_FULL + b], static_cast<uint32_t>((g >> 1) & 1), wctx, AB_P_FULL + b);
-                        TRACE(6, g);
                         tc_fence_after();
                         const uint32_t v_addr = smem_u32(kv_smem + s * A_STAGE_BYTES + A_KV_BYTES);
                         const uint32_t d = tmem_base + A_COL_O + qb * A_D;
@@ -381,7 +367,6 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                             mma_f16_ts(d, p_tmem + kk * 8, make_smem_desc_sw128(v_addr + kk * 2048, 16, 1024), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
                         tc_commit(&bars[AB_KV_EMPTY + s]);
                         tc_commit(&bars[AB_PV_DONE + b]);
-                        TRACE(7, g);
                     }
                     ++it;
                     n = n_next;
@@ -453,15 +438,12 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     const int b = static_cast<int>(g & 1);
                     const uint2 cur = cw;
                     if (j + 1 < n) cw = __ldg(my_codes + (j + 1) * 8);     // 32 codes = 64 B = 8 uint2 per tile
-                    if (threadIdx.x == 0) TRACE(0, g);
                     mbar_wait(&bars[AB_S_FULL + b], static_cast<uint32_t>((g >> 1) & 1), wctx, AB_S_FULL + b);
-                    if (threadIdx.x == 0) TRACE(1, g);
                     tc_fence_after();
                     uint32_t r0[32], r1[32];
                     tmem_ld32(t_lane + A_COL_S + b * A_TKV, r0);
                     tmem_ld32(t_lane + A_COL_S + b * A_TKV + 32, r1);
                     tc_wait_ld();
-                    if (threadIdx.x == 0) TRACE(2, g);
 
                     const bool all_absent = (cur.x | cur.y) == 0u;
                     const bool all_full = cur.x == 0x00010001u && cur.y == 0x00010001u;
@@ -587,20 +569,16 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     }
                     // P overlays the first 32 columns of the S buffer it was computed from; the QK^T that next writes this
                     // buffer is issued after the PV product that reads P and the tensor core executes them in that order
-                    if (threadIdx.x == 0) TRACE(3, g);
                     tmem_st32(t_lane + A_COL_S + b * A_TKV, r0);
                     tc_wait_st();
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bars[AB_P_FULL + b]);
-                    if (threadIdx.x == 0) TRACE(4, g);
                 }
                 // ---------------------------------------------------------- item epilogue: O / l -> fp16 -> global
                 {
                     const int pb = static_cast<int>((g - 1) & 1);
-                    if (threadIdx.x == 0) TRACE(0, 128 + it);
                     mbar_wait(&bars[AB_PV_DONE + pb], static_cast<uint32_t>(((g - 1) >> 1) & 1), wctx, AB_PV_DONE + pb);
-                    if (threadIdx.x == 0) TRACE(1, 128 + it);
                     tc_fence_after();
                     uint32_t o0[32], o1[32];
                     tmem_ld32(t_lane + A_COL_O + ob * A_D, o0);
@@ -609,7 +587,6 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bars[AB_O_FREE + ob]);
-                    if (threadIdx.x == 0) TRACE(2, 128 + it);
                     {
                         const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.0f;
                         uint4 u[8];
@@ -623,7 +600,6 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                         }
                         store_rows(u, cur_item);
                     }
-                    if (threadIdx.x == 0) TRACE(3, 128 + it);
                 }
                 ++it;
             }
@@ -687,13 +663,6 @@ int check_blocks(int seq_len, int block_m, int block_n) {
 
 using namespace stof;
 
-#ifdef STOF_TRACE
-long long* g_trace_ptr = nullptr;
-extern "C" int stof_trace_read(long long* host, int n) {
-    cudaDeviceSynchronize();
-    return static_cast<int>(cudaMemcpy(host, g_trace_ptr, n * sizeof(long long), cudaMemcpyDeviceToHost));
-}
-#endif
 
 extern "C" size_t stof_block_attn_plan_bytes(int seq_len, int block_m, int block_n) {
     if (seq_len <= 0 || block_m <= 0 || block_n <= 0) return 0;
@@ -764,16 +733,6 @@ extern "C" int stof_block_attn(const void* q, const void* k, const void* v, void
     STOF_REQUIRE(items < (1ll << 31), "block_attn: batch * heads * query tiles beyond 2^31");
     p.total_items = static_cast<unsigned>(items);
     p.bh_total = static_cast<unsigned>(batch) * static_cast<unsigned>(heads);
-#ifdef STOF_TRACE
-    {
-        static long long* trace_buf = nullptr;
-        if (!trace_buf) cudaMalloc(&trace_buf, 256 * 8 * sizeof(long long));
-        cudaMemsetAsync(trace_buf, 0, 256 * 8 * sizeof(long long), stream);
-        p.trace = trace_buf;
-        extern long long* g_trace_ptr;
-        g_trace_ptr = trace_buf;
-    }
-#endif
     CUtensorMap mq, mk, mv, mo;
     if (int rc = make_qkv_map(&mo, out, batch, heads, seq_len, out_strides, 32, &p.slot_s[3], &p.slot_h[3], &p.slot_b[3])) return rc;
     if (int rc = make_qkv_map(&mq, q, batch, heads, seq_len, q_strides, A_TQ, &p.slot_s[0], &p.slot_h[0], &p.slot_b[0])) return rc;

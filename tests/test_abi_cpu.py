@@ -106,7 +106,9 @@ def test_drop_in_module_names_import():
     import triton_template.gemm_gemm as t2
     import triton_template.add_layernorm as t3
     import block_attn_mask as ext
+    import rowwise_attn_full as r1, rowwise_attn_sliding as r2, rowwise_attn_mask as r3
     assert callable(po.block_attn_mask_op) and callable(ext.forward)
+    assert all(callable(f) for f in (po.rowwise_attn_full_op, po.rowwise_attn_sliding_op, po.rowwise_attn_mask_op, r1.forward, r2.forward, r3.forward))
     assert callable(um.get_sparse_storage) and callable(um.generate_bigbird_mask)
     assert callable(uu.transpose_for_scores) and callable(uu.time_stamp_cudasync)
     assert callable(t1.triton_matmul_bias_layernorm) and callable(t2.triton_matmul_batch) and callable(t3.triton_batched_bias_layernorm)

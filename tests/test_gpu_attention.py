@@ -159,3 +159,28 @@ def test_bad_inputs_raise():
     q = torch.zeros(1, 1, 128, 64, dtype=torch.float16, device="cuda")
     with pytest.raises(stof_b200.StofError):
         stof_b200.block_attn_mask(q.transpose(1, 2), q, q, *idx, 64, 64, 4)
+
+
+def test_rowwise_operators_match_their_oracles():
+    from ops.package_op import rowwise_attn_full_op, rowwise_attn_mask_op, rowwise_attn_sliding_op
+    import rowwise_attn_full as ext_full
+    B, H, S = 2, 5, 256                                  # 5 heads: not a multiple of 3, every head must still be computed
+    q, k, v = _qkv(B, H, S, seed=33)
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    for causal in (False, True):
+        got = rowwise_attn_full_op(qd, kd, vd, causal)
+        assert got.shape == (B, S, H * 64) and _err(got.float().cpu(), oa.rowwise_full(q, k, v, causal)) <= TOL
+        got = rowwise_attn_sliding_op(qd, kd, vd, causal, 37)
+        assert _err(got.float().cpu(), oa.rowwise_sliding(q, k, v, causal, 37)) <= TOL
+    rm = torch.from_numpy(om.generate_dilated_mask(1, S, 24, 1, False, np.float16)[0])
+    rm = torch.clamp(rm + torch.eye(S, dtype=torch.float16), max=1)       # every row keeps a key (the reference divides 0/0 otherwise)
+    got = rowwise_attn_mask_op(qd, kd, vd, False, rm.cuda())
+    assert _err(got.float().cpu(), oa.rowwise_mask(q, k, v, False, rm)) <= TOL
+    got = rowwise_attn_mask_op(qd, kd, vd, True, (rm * 3).cuda())          # any positive value admits a key
+    assert _err(got.float().cpu(), oa.rowwise_mask(q, k, v, True, rm)) <= TOL
+    res = torch.zeros(B, S, H * 64, dtype=torch.float16, device="cuda")
+    ext_full.forward(qd, kd, vd, True, res)                                 # extension-module form: result pre-allocated by the caller
+    assert _err(res.float().cpu(), oa.rowwise_full(q, k, v, True)) <= TOL
+    q48, k48, v48 = _qkv(1, 3, 48, seed=34)                                 # S = 48: 16-wide blocks
+    got = rowwise_attn_full_op(q48.cuda(), k48.cuda(), v48.cuda(), True)
+    assert _err(got.float().cpu(), oa.rowwise_full(q48, k48, v48, True)) <= TOL
