@@ -452,13 +452,13 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     // every 8 pairs take the FMA-pipe polynomial instead of the MUFU unit.  The fp16 pairs of P are written over
                     // r0 as its scores are consumed.  Returns the row sum of this tile.
                     auto exp_tile = [&](float neg_m) -> float {
-                        const uint64_t scale2 = pk2(scale, scale), negm2 = pk2(neg_m, neg_m);
-                        uint64_t sum_a = pk2(0.f, 0.f), sum_b = pk2(0.f, 0.f);
+                        const float2 scale2 = pk2(scale, scale), negm2 = pk2(neg_m, neg_m);
+                        float2 sum_a = pk2(0.f, 0.f), sum_b = pk2(0.f, 0.f);
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
                             const uint32_t lo = (i < 16) ? r0[2 * i] : r1[2 * (i - 16)];
                             const uint32_t hi = (i < 16) ? r0[2 * i + 1] : r1[2 * (i - 16) + 1];
-                            const uint64_t x2 = fma2(pk2(__uint_as_float(lo), __uint_as_float(hi)), scale2, negm2);
+                            const float2 x2 = fma2(pk2(__uint_as_float(lo), __uint_as_float(hi)), scale2, negm2);
                             float e0, e1;
                             if ((i & 7) < A_POLY_PAIRS) {
                                 exp2_poly_pair(x2, e0, e1);

@@ -32,11 +32,11 @@ enum { BAR_FULL = 0, BAR_EMPTY = G_STAGES, BAR_TFULL = 2 * G_STAGES, BAR_TEMPTY 
 // erf-form GELU on a packed pair: 0.5 x (1 + erf(x / sqrt 2)) with erf(z) = sign(z) (1 - 1 / p(|z|)^16),
 // p a degree-6 polynomial (Abramowitz & Stegun 7.1.28, |error| <= 3e-7): six packed FMAs, four packed squarings and one
 // reciprocal per element instead of the ~30 instructions of erff.
-__device__ __forceinline__ uint64_t gelu_erf2(uint64_t x2) {
+__device__ __forceinline__ float2 gelu_erf2(float2 x2) {
     float x0, x1;
     upk2(x2, x0, x1);
-    const uint64_t z = pk2(fabsf(x0) * 0.70710678118654752f, fabsf(x1) * 0.70710678118654752f);
-    uint64_t p = fma2(pk2(0.0000430638f, 0.0000430638f), z, pk2(0.0002765672f, 0.0002765672f));
+    const float2 z = pk2(fabsf(x0) * 0.70710678118654752f, fabsf(x1) * 0.70710678118654752f);
+    float2 p = fma2(pk2(0.0000430638f, 0.0000430638f), z, pk2(0.0002765672f, 0.0002765672f));
     p = fma2(p, z, pk2(0.0001520143f, 0.0001520143f));
     p = fma2(p, z, pk2(0.0092705272f, 0.0092705272f));
     p = fma2(p, z, pk2(0.0422820123f, 0.0422820123f));
@@ -50,13 +50,13 @@ __device__ __forceinline__ uint64_t gelu_erf2(uint64_t x2) {
     upk2(p, p0, p1);
     const float e0 = copysignf(1.0f - __fdividef(1.0f, p0), x0);      // p^16 = inf for large |x| gives erf = +-1
     const float e1 = copysignf(1.0f - __fdividef(1.0f, p1), x1);
-    const uint64_t hx = mul2(x2, pk2(0.5f, 0.5f));
+    const float2 hx = mul2(x2, pk2(0.5f, 0.5f));
     return fma2(hx, pk2(e0, e1), hx);
 }
 // tanh-form GELU: 0.5 x (1 + tanh(u)) = x * sigmoid(2u), u = 0.79788456 (x + 0.044715 x^3)
-__device__ __forceinline__ uint64_t gelu_tanh2(uint64_t x2) {
-    const uint64_t xx = mul2(x2, x2);
-    const uint64_t inner = fma2(xx, pk2(0.044715f * 0.7978845608028654f, 0.044715f * 0.7978845608028654f),
+__device__ __forceinline__ float2 gelu_tanh2(float2 x2) {
+    const float2 xx = mul2(x2, x2);
+    const float2 inner = fma2(xx, pk2(0.044715f * 0.7978845608028654f, 0.044715f * 0.7978845608028654f),
                                 pk2(0.7978845608028654f, 0.7978845608028654f));
     float u0, u1, x0, x1;
     upk2(mul2(inner, x2), u0, u1);
@@ -204,7 +204,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                         for (int g = 0; g < 8; ++g) {                     // 8 columns = one 16-byte chunk of the output row
                             const uint32_t* src = (g < 4) ? &r0[8 * g] : &r1[8 * (g - 4)];
                             const int col = col0 + 8 * g;
-                            uint64_t v[4];
+                            float2 v[4];
 #pragma unroll
                             for (int j = 0; j < 4; ++j) v[j] = pk2(__uint_as_float(src[2 * j]), __uint_as_float(src[2 * j + 1]));
                             if (bias != nullptr && col < n) {

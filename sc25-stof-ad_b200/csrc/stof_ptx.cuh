@@ -255,33 +255,13 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// Packed fp32 pairs in one 64-bit register (add / sub / fma on both halves in one instruction).
-__device__ __forceinline__ uint64_t pk2(float lo, float hi) {
-    uint64_t r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-    return r;
-}
-__device__ __forceinline__ void upk2(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
-__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
-    uint64_t d;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-    return d;
-}
-__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
-    uint64_t d;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
-__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
-    uint64_t d;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
-__device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) {
-    uint64_t d;
-    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
+// Packed fp32 pairs (one 64-bit register pair; add / mul / fma on both halves in one instruction on sm_100).
+__device__ __forceinline__ float2 pk2(float lo, float hi) { return make_float2(lo, hi); }
+__device__ __forceinline__ void upk2(float2 v, float& lo, float& hi) { lo = v.x; hi = v.y; }
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 sub2(float2 a, float2 b) { return __ffma2_rn(b, make_float2(-1.0f, -1.0f), a); }
 
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
@@ -293,16 +273,16 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // 1.5 * 2^23 magic add, degree-3 minimax polynomial for 2^f (max relative error 7.5e-5, far below the
 // 4.9e-4 quantisation of the fp16 value it feeds), exponent inserted with an integer shift-add.
 // Inputs below -126 are clamped (the result is then ~1e-38 instead of 0).
-__device__ __forceinline__ void exp2_poly_pair(uint64_t x2, float& e0, float& e1) {
+__device__ __forceinline__ void exp2_poly_pair(float2 x2, float& e0, float& e1) {
     float x0, x1;
     upk2(x2, x0, x1);
     x0 = fmaxf(x0, -126.0f);
     x1 = fmaxf(x1, -126.0f);
-    const uint64_t xc = pk2(x0, x1);
-    const uint64_t magic = pk2(12582912.0f, 12582912.0f);
-    const uint64_t xf = add2(xc, magic);
-    const uint64_t fr = sub2(xc, sub2(xf, magic));
-    uint64_t p = fma2(pk2(0.0551716685295105f, 0.0551716685295105f), fr, pk2(0.2426111251115799f, 0.2426111251115799f));
+    const float2 xc = pk2(x0, x1);
+    const float2 magic = pk2(12582912.0f, 12582912.0f);
+    const float2 xf = add2(xc, magic);
+    const float2 fr = add2(xc, fma2(xf, pk2(-1.0f, -1.0f), magic));      // x - round(x): magic - xf is exact
+    float2 p = fma2(pk2(0.0551716685295105f, 0.0551716685295105f), fr, pk2(0.2426111251115799f, 0.2426111251115799f));
     p = fma2(p, fr, pk2(0.6932609677314758f, 0.6932609677314758f));
     p = fma2(p, fr, pk2(0.9999280571937561f, 0.9999280571937561f));
     float p0, p1, f0, f1;
