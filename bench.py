@@ -220,6 +220,7 @@ def run_attention(args, rank, world, local):
     value = total_flops / (ms_per_step * 1e-3) / 1e12
 
     if args.kernel_only:
+        args.no_encoder = True
         if rank == 0:
             print(json.dumps({"metric": "masked-MHA effective TFLOP/s", "value": value, "unit": "TFLOP/s", "ms_per_step": ms_per_step,
                               "config": {"workload": cfg.name, "load_blocks": n_load}, "note": "kernel-only run (profiling aid)"}))
@@ -248,6 +249,12 @@ def run_attention(args, rank, world, local):
     h2d = 3 * q_h.numel() * 2
     d2h = out_h.numel() * 2
 
+    encoder = None
+    alg_bytes = 4 * q.numel() * 2
+    if not args.no_encoder:
+        q = k = v = out = flush = None
+        torch.cuda.empty_cache()
+        encoder = encoder_measure(args, rank, world, local, steps=max(2, min(args.steps, 3)), warmup=3)
     if rank != 0:
         return 0
     # parity spot check of the timed output against the oracle is the job of the tests; here only sanity
@@ -267,7 +274,7 @@ def run_attention(args, rank, world, local):
                    "l2": "256 MiB flush write between timed steps", "parallelism": f"independent batch shards x{world}"},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
                      "traffic": traffic, "traffic_unit": "bytes per launch (ncu dram read+write, batch-8 capture scaled)",
-                     "algorithmic_bytes": 4 * q.numel() * 2, "peak_source": peaks["source"] + " bf16 burst",
+                     "algorithmic_bytes": alg_bytes, "peak_source": peaks["source"] + " bf16 burst",
                      "frac_of_sustained": achieved / peaks["tflops_sustained"], "kernel": "block_attn_kernel"},
         "cpu_baseline": {"value": cpu_val, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port", "sample": cpu_desc,
                          "seconds": cpu_s},
@@ -278,8 +285,50 @@ def run_attention(args, rank, world, local):
                        "note": "classify + fill + host read of the three totals, S=%d" % cfg.seq_len},
         "wall_s_timed_region": wall, "output_finite": finite,
     }
+    if encoder is not None:
+        line["encoder"] = encoder
     print(json.dumps(line))
     return 0
+
+
+def encoder_measure(args, rank, world, local, steps, warmup):
+    """BERT-large 24-layer forward (config 5), the configuration's batch of 64 sharded over the ranks (strong scaling);
+    returns the dict that the attention line carries under "encoder" (None on ranks other than 0)."""
+    import stof_b200
+    from stof_b200 import _lib, dist as sd, workloads as wl
+    dev = torch.device("cuda", local)
+    cfg = wl.ENCODER_CONFIGS["cfg5"]
+    lo, hi = sd.shard_range(cfg.batch, rank, world)
+    x = wl.encoder_input(cfg, (lo, hi)).to(dev)
+    layers = [stof_b200.EncoderWeights.from_dict(p, dev) for p in wl.encoder_weights(cfg)]
+    enc = stof_b200.BertEncoder(layers, cfg.heads, cfg.eps, "erf", cfg.block, cfg.block)
+    idx = enc.set_mask(wl.config_mask(cfg).to(dev))
+    n_load = int(idx[5][-1].item())
+    for _ in range(warmup):
+        enc(x)
+    torch.cuda.synchronize(dev)
+    _lib.check_status(dev, "encoder warm-up")
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if world > 1:
+        torch.distributed.barrier()
+    torch.cuda.synchronize(dev)
+    e0.record()
+    for _ in range(steps):
+        enc(x)
+    e1.record()
+    torch.cuda.synchronize(dev)
+    if world > 1:
+        torch.distributed.barrier()
+    _lib.check_status(dev, "encoder timed region")
+    ms = sd.max_over_ranks(e0.elapsed_time(e1), dev) / steps
+    if rank != 0:
+        return None
+    peaks = measured_peaks()
+    tflops = wl.encoder_flops(cfg, n_load, cfg.batch) / (ms * 1e-3) / 1e12
+    return {"metric": "BERT encoder tokens/s", "value": cfg.batch * cfg.seq_len / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
+            "steps": steps, "warmup": warmup, "scaling": "strong", "workload": cfg.name, "global_batch": cfg.batch, "seq_len": cfg.seq_len,
+            "layers": cfg.layers, "load_blocks": n_load, "tflops_all_gpus": tflops,
+            "frac_of_sustained_peak_per_gpu": tflops / world / peaks["tflops_sustained"], "gpu_launches": steps * cfg.layers * 7}
 
 
 def run_encoder(args, rank, world, local):
@@ -357,6 +406,7 @@ def main():
     ap.add_argument("--impl", default="stof", choices=["stof", "reference"])
     ap.add_argument("--workload", default="attention", choices=["attention", "encoder"])
     ap.add_argument("--batch", type=int, default=0, help="override the batch size (profiling aid: smaller captures)")
+    ap.add_argument("--no-encoder", action="store_true", help="skip the BERT-large encoder forward that the attention run reports under 'encoder'")
     ap.add_argument("--kernel-only", action="store_true", help="skip the end-to-end and CPU-baseline legs (profiling aid)")
     ap.add_argument("--config", default=None, help="cfg2 (default) or cfg3 for attention; cfg5 (default) or cfg4 for the encoder")
     args = ap.parse_args()

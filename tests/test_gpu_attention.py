@@ -184,3 +184,31 @@ def test_rowwise_operators_match_their_oracles():
     q48, k48, v48 = _qkv(1, 3, 48, seed=34)                                 # S = 48: 16-wide blocks
     got = rowwise_attn_full_op(q48.cuda(), k48.cuda(), v48.cuda(), True)
     assert _err(got.float().cpu(), oa.rowwise_full(q48, k48, v48, True)) <= TOL
+
+
+@pytest.mark.parametrize("B,H", [(3, 7), (5, 9), (1, 1)])
+def test_scheduler_groups_and_tails(B, H):
+    """Batch x heads below, above and not a multiple of the scheduler's (batch, head) group size, with a mask whose query
+    tiles differ in length (so that the visiting order is a real permutation)."""
+    S = 512
+    q, k, v = _qkv(B, H, S, seed=B * 31 + H)
+    bm = om.block_sliding(S // 64, 1)
+    bm[0, :] = 1
+    bm[:, 0] = 1
+    bm[5, 2] = 1
+    mask = om.expand_block_mask(bm)
+    got = _run_op(q, k, v, _index(mask, 64, 64), 64, 64)
+    want = oa.masked_attention_fp32(q, k, v, torch.from_numpy(mask.astype(np.float32)))
+    assert _err(got, want) <= TOL
+
+
+def test_back_to_back_calls_with_different_indices_share_nothing():
+    B, H, S = 1, 2, 256
+    q, k, v = _qkv(B, H, S, seed=77)
+    m1 = om.generate_causal_mask(1, S)
+    m2 = om.expand_block_mask(om.block_sliding(4, 1))
+    i1, i2 = _index(m1, 32, 32), _index(m2, 64, 64)
+    for mask, idx, blk in ((m1, i1, 32), (m2, i2, 64), (m1, i1, 32)):
+        got = _run_op(q, k, v, idx, blk, blk)
+        want = oa.masked_attention_fp32(q, k, v, torch.from_numpy(np.asarray(mask, dtype=np.float32)))
+        assert _err(got, want) <= TOL

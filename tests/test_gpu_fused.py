@@ -118,3 +118,21 @@ def test_encoder_config4_shape_one_layer_slice():
     torch.cuda.synchronize()
     want = of.bert_layer(hidden, params[0], torch.from_numpy(mask.astype(np.float32)), heads, eps=1e-12)
     assert _err(got, want) <= 2e-3 * max(1.0, want.abs().max().item())
+
+
+def test_two_layer_encoder_random_affine():
+    """Two stacked layers with random gamma/beta/biases, BigBird-style block mask with a partial (causal) variant."""
+    import stof_b200
+    B, S, hid, heads, ffn = 2, 256, 256, 4, 512
+    params = of.make_bert_params(hid, ffn, 2, seed=9, random_affine=True)
+    g = torch.Generator().manual_seed(9)
+    hidden = torch.randn(B, S, hid, generator=g).half()
+    mask = om.generate_sliding_mask(1, S, 70, False, np.float16)
+    enc = stof_b200.BertEncoder([stof_b200.EncoderWeights.from_dict(p, "cuda") for p in params], head_num=heads, eps=1e-12)
+    enc.set_mask(torch.from_numpy(mask).cuda())
+    got = enc(hidden.cuda()).clone()
+    torch.cuda.synchronize()
+    want = of.encoder_forward(hidden, params, torch.from_numpy(mask.astype(np.float32)), heads, 1e-12)
+    assert _err(got, want) <= 3e-3 * max(1.0, want.abs().max().item())     # two layers of fp16 storage
+    again = enc(hidden.cuda())
+    assert torch.equal(again, got)                                          # deterministic, buffers reused
