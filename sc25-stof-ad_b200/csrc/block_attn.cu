@@ -223,6 +223,59 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     return d;
 }
 
+// Rare paths of the softmax loop are kept out of line (and work on tensor memory, not on the caller's register arrays) so that
+// the loop the warps spend their time in stays a few kilobytes of straight-line code.
+
+// Applies the block mask to the 32 x 64 scores of one warp in place: column groups a row does not list become -inf, partial
+// groups get their -10000 * (1 - mask) addend.  `cx`, `cy` hold this thread's four group codes.
+__device__ __noinline__ void mask_scores_in_tmem(uint32_t t_s, uint32_t cx, uint32_t cy, const __half* part_block_mask, int part_base, int bm_shift,
+                                                 int bn, int row_in_block, int col0) {
+    const unsigned code[4] = {cx & 0xFFFFu, cx >> 16, cy & 0xFFFFu, cy >> 16};
+#pragma unroll 1
+    for (int cg = 0; cg < 4; ++cg) {
+        const unsigned c = code[cg];
+        if (__all_sync(0xffffffffu, c == 1u)) continue;
+        uint32_t v[16];
+        tmem_ld16(t_s + cg * 16, v);
+        tc_wait_ld();
+        if (c == 0u) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = 0xFF800000u;      // -inf
+        } else if (c >= 2u) {
+            const int col_in_block = (col0 + cg * 16) & (bn - 1);
+            const __half* mp = part_block_mask + ((static_cast<size_t>(part_base + c - 2) << bm_shift) + row_in_block) * bn + col_in_block;
+            const uint4 u0 = __ldg(reinterpret_cast<const uint4*>(mp));
+            const uint4 u1 = __ldg(reinterpret_cast<const uint4*>(mp + 8));
+            const __half2* h0 = reinterpret_cast<const __half2*>(&u0);
+            const __half2* h1 = reinterpret_cast<const __half2*>(&u1);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 a = __half22float2(h0[i]), b = __half22float2(h1[i]);
+                v[2 * i] = __float_as_uint(__uint_as_float(v[2 * i]) + a.x);
+                v[2 * i + 1] = __float_as_uint(__uint_as_float(v[2 * i + 1]) + a.y);
+                v[8 + 2 * i] = __float_as_uint(__uint_as_float(v[8 + 2 * i]) + b.x);
+                v[8 + 2 * i + 1] = __float_as_uint(__uint_as_float(v[8 + 2 * i + 1]) + b.y);
+            }
+        }
+        tmem_st16(t_s + cg * 16, v);
+    }
+    tc_wait_st();
+}
+
+// O *= alpha for this thread's row (64 fp32 columns in tensor memory)
+__device__ __noinline__ void rescale_o_in_tmem(uint32_t t_o, float alpha) {
+#pragma unroll 1
+    for (int c = 0; c < A_D; c += 16) {
+        uint32_t o[16];
+        tmem_ld16(t_o + c, o);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+        tmem_st16(t_o + c, o);
+    }
+    tc_wait_st();
+}
+
 __global__ void __launch_bounds__(A_THREADS, A_CTAS_PER_SM)
 block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                   const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o, const AttnParams p) {
@@ -438,20 +491,54 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     const int b = static_cast<int>(g & 1);
                     const uint2 cur = cw;
                     if (j + 1 < n) cw = __ldg(my_codes + (j + 1) * 8);     // 32 codes = 64 B = 8 uint2 per tile
+                    const bool all_absent = (cur.x | cur.y) == 0u;
+                    const bool all_full = cur.x == 0x00010001u && cur.y == 0x00010001u;
+                    const bool warp_absent = __all_sync(0xffffffffu, all_absent);
+                    const bool warp_full = __all_sync(0xffffffffu, all_full);
                     mbar_wait(&bars[AB_S_FULL + b], static_cast<uint32_t>((g >> 1) & 1), wctx, AB_S_FULL + b);
                     tc_fence_after();
                     uint32_t r0[32], r1[32];
-                    tmem_ld32(t_lane + A_COL_S + b * A_TKV, r0);
-                    tmem_ld32(t_lane + A_COL_S + b * A_TKV + 32, r1);
-                    tc_wait_ld();
-
-                    const bool all_absent = (cur.x | cur.y) == 0u;
-                    const bool all_full = cur.x == 0x00010001u && cur.y == 0x00010001u;
-
-                    // P = 2^(s * scale - m) for the 64 scores in r0/r1: pairs of columns with packed fp32 FMAs; A_POLY_PAIRS of
-                    // every 8 pairs take the FMA-pipe polynomial instead of the MUFU unit.  The fp16 pairs of P are written over
-                    // r0 as its scores are consumed.  Returns the row sum of this tile.
-                    auto exp_tile = [&](float neg_m) -> float {
+                    if (warp_absent) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) r0[i] = 0u;
+                    } else {
+                        if (!warp_full)
+                            mask_scores_in_tmem(t_lane + A_COL_S + b * A_TKV, cur.x, cur.y, p.part_block_mask, part_base, p.bm_shift, p.bn, row_in_block,
+                                                static_cast<int>(tl[j]) * A_TKV);
+                        tmem_ld32(t_lane + A_COL_S + b * A_TKV, r0);
+                        tmem_ld32(t_lane + A_COL_S + b * A_TKV + 32, r1);
+                        tc_wait_ld();
+                        // row maximum of the raw scores (four independent chains of 3-input maxima), then in log2 units
+                        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) {
+                            mx0 = max3(mx0, __uint_as_float(r0[i]), __uint_as_float(r1[i]));
+                            mx1 = max3(mx1, __uint_as_float(r0[i + 1]), __uint_as_float(r1[i + 1]));
+                            mx2 = max3(mx2, __uint_as_float(r0[i + 2]), __uint_as_float(r1[i + 2]));
+                            mx3 = max3(mx3, __uint_as_float(r0[i + 3]), __uint_as_float(r1[i + 3]));
+                        }
+                        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale;
+                        // lazy rescale: move the reference maximum only when it would grow by more than the threshold
+                        const bool need = mx > m_ref + A_RESCALE_THRESHOLD || (m_ref == -INFINITY && mx > -INFINITY);
+                        if (__any_sync(0xffffffffu, need)) {
+                            float alpha = 1.0f;
+                            if (need) {
+                                alpha = (m_ref == -INFINITY) ? 0.0f : fast_exp2(m_ref - mx);
+                                m_ref = mx;
+                                l_sum *= alpha;
+                            }
+                            if (j > 0) {
+                                // every PV product issued so far for this item must have landed in O before it is rescaled
+                                const int pb = static_cast<int>((g - 1) & 1);
+                                mbar_wait(&bars[AB_PV_DONE + pb], static_cast<uint32_t>(((g - 1) >> 1) & 1), wctx, AB_PV_DONE + pb);
+                                tc_fence_after();
+                                rescale_o_in_tmem(t_lane + A_COL_O + ob * A_D, alpha);
+                            }
+                        }
+                        // P = 2^(s * scale - m) for the 64 scores in r0/r1: pairs of columns with packed fp32 FMAs; A_POLY_PAIRS of
+                        // every 8 pairs take the FMA-pipe polynomial instead of the MUFU unit.  The fp16 pairs of P are written over
+                        // r0 as its scores are consumed.
+                        const float neg_m = (m_ref == -INFINITY) ? 0.0f : -m_ref;
                         const float2 scale2 = pk2(scale, scale), negm2 = pk2(neg_m, neg_m);
                         float2 sum_a = pk2(0.f, 0.f), sum_b = pk2(0.f, 0.f);
 #pragma unroll
@@ -474,98 +561,7 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                         }
                         float sa0, sa1;
                         upk2(add2(sum_a, sum_b), sa0, sa1);
-                        return sa0 + sa1;
-                    };
-
-                    if (__all_sync(0xffffffffu, all_absent)) {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) r0[i] = 0u;
-                    } else {
-                        const bool warp_full = __all_sync(0xffffffffu, all_full);
-                        // Speculative step: a fully listed tile is exponentiated against the current reference maximum without
-                        // a maximum pass.  It stands if every row sum stays below 2^8 (no exponent beyond the lazy-rescale
-                        // threshold can hide in such a sum; infinities and NaNs fail the test too); otherwise the scores are
-                        // read again and the exact path below runs.
-                        bool done = false;
-                        if (warp_full && j > 0 && __all_sync(0xffffffffu, m_ref != -INFINITY)) {
-                            const float tile_sum = exp_tile(-m_ref);
-                            if (__all_sync(0xffffffffu, tile_sum <= 256.0f)) {
-                                l_sum += tile_sum;
-                                done = true;
-                            } else {
-                                tmem_ld32(t_lane + A_COL_S + b * A_TKV, r0);
-                                tmem_ld32(t_lane + A_COL_S + b * A_TKV + 32, r1);
-                                tc_wait_ld();
-                            }
-                        }
-                        if (!done) {
-                            if (!warp_full) {
-                                const int tile = tl[j];
-                                const unsigned code[4] = {cur.x & 0xFFFFu, cur.x >> 16, cur.y & 0xFFFFu, cur.y >> 16};
-#pragma unroll
-                                for (int cg = 0; cg < 4; ++cg) {
-                                    uint32_t* dstv = (cg < 2) ? &r0[16 * cg] : &r1[16 * (cg - 2)];
-                                    if (code[cg] == 0u) {
-#pragma unroll
-                                        for (int i = 0; i < 16; ++i) dstv[i] = 0xFF800000u;      // -inf
-                                    } else if (code[cg] >= 2u) {
-                                        const int col_in_block = (tile * A_TKV + cg * 16) & (p.bn - 1);
-                                        const __half* mp = p.part_block_mask +
-                                                           ((static_cast<size_t>(part_base + code[cg] - 2) << p.bm_shift) + row_in_block) * p.bn + col_in_block;
-                                        const uint4 u0 = __ldg(reinterpret_cast<const uint4*>(mp));
-                                        const uint4 u1 = __ldg(reinterpret_cast<const uint4*>(mp + 8));
-                                        const __half2* h0 = reinterpret_cast<const __half2*>(&u0);
-                                        const __half2* h1 = reinterpret_cast<const __half2*>(&u1);
-#pragma unroll
-                                        for (int i = 0; i < 4; ++i) {
-                                            const float2 a = __half22float2(h0[i]), c2 = __half22float2(h1[i]);
-                                            dstv[2 * i] = __float_as_uint(__uint_as_float(dstv[2 * i]) + a.x);
-                                            dstv[2 * i + 1] = __float_as_uint(__uint_as_float(dstv[2 * i + 1]) + a.y);
-                                            dstv[8 + 2 * i] = __float_as_uint(__uint_as_float(dstv[8 + 2 * i]) + c2.x);
-                                            dstv[8 + 2 * i + 1] = __float_as_uint(__uint_as_float(dstv[8 + 2 * i + 1]) + c2.y);
-                                        }
-                                    }
-                                }
-                            }
-                            // row maximum of the raw scores (four independent chains of 3-input maxima), then in log2 units
-                            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-                            for (int i = 0; i < 32; i += 4) {
-                                mx0 = max3(mx0, __uint_as_float(r0[i]), __uint_as_float(r1[i]));
-                                mx1 = max3(mx1, __uint_as_float(r0[i + 1]), __uint_as_float(r1[i + 1]));
-                                mx2 = max3(mx2, __uint_as_float(r0[i + 2]), __uint_as_float(r1[i + 2]));
-                                mx3 = max3(mx3, __uint_as_float(r0[i + 3]), __uint_as_float(r1[i + 3]));
-                            }
-                            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale;
-                            // lazy rescale: move the reference maximum only when it would grow by more than the threshold
-                            const bool need = mx > m_ref + A_RESCALE_THRESHOLD || (m_ref == -INFINITY && mx > -INFINITY);
-                            if (__any_sync(0xffffffffu, need)) {
-                                float alpha = 1.0f;
-                                if (need) {
-                                    alpha = (m_ref == -INFINITY) ? 0.0f : fast_exp2(m_ref - mx);
-                                    m_ref = mx;
-                                    l_sum *= alpha;
-                                }
-                                if (j > 0) {
-                                    const int pb = static_cast<int>((g - 1) & 1);
-                                    mbar_wait(&bars[AB_PV_DONE + pb], static_cast<uint32_t>(((g - 1) >> 1) & 1), wctx, AB_PV_DONE + pb);
-                                    tc_fence_after();
-                                    uint32_t o0[32], o1[32];
-                                    tmem_ld32(t_lane + A_COL_O + ob * A_D, o0);
-                                    tmem_ld32(t_lane + A_COL_O + ob * A_D + 32, o1);
-                                    tc_wait_ld();
-#pragma unroll
-                                    for (int i = 0; i < 32; ++i) {
-                                        o0[i] = __float_as_uint(__uint_as_float(o0[i]) * alpha);
-                                        o1[i] = __float_as_uint(__uint_as_float(o1[i]) * alpha);
-                                    }
-                                    tmem_st32(t_lane + A_COL_O + ob * A_D, o0);
-                                    tmem_st32(t_lane + A_COL_O + ob * A_D + 32, o1);
-                                    tc_wait_st();
-                                }
-                            }
-                            l_sum += exp_tile((m_ref == -INFINITY) ? 0.0f : -m_ref);
-                        }
+                        l_sum += sa0 + sa1;
                     }
                     // P overlays the first 32 columns of the S buffer it was computed from; the QK^T that next writes this
                     // buffer is issued after the PV product that reads P and the tensor core executes them in that order
