@@ -431,7 +431,7 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             const int lr = warp * 32 + lane;                 // local row = tensor-memory lane
             const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
             const int rg = lr >> 4;                          // 16-row group inside the query tile
-            const float scale = p.scale_log2;
+            const float scale = p.scale_log2, inv_scale = 1.0f / p.scale_log2;
             long long g = 0;
             int it = 0;
             // per-item values that need global loads are fetched one item ahead (no dependent-load chain at item boundaries)
@@ -523,8 +523,10 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                         if (__any_sync(0xffffffffu, need)) {
                             float alpha = 1.0f;
                             if (need) {
-                                alpha = (m_ref == -INFINITY) ? 0.0f : fast_exp2(m_ref - mx);
-                                m_ref = mx;
+                                // the reference is kept integer-valued (the polynomial exponential folds it into its rounding constant)
+                                const float m_new = fminf(fmaxf(ceilf(mx), -2097152.0f), 2097152.0f);
+                                alpha = (m_ref == -INFINITY) ? 0.0f : fast_exp2(m_ref - m_new);
+                                m_ref = m_new;
                                 l_sum *= alpha;
                             }
                             if (j > 0) {
@@ -540,18 +542,19 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                         // r0 as its scores are consumed.
                         const float neg_m = (m_ref == -INFINITY) ? 0.0f : -m_ref;
                         const float2 scale2 = pk2(scale, scale), negm2 = pk2(neg_m, neg_m);
+                        const float2 mm2 = pk2(12582912.0f + neg_m, 12582912.0f + neg_m);
+                        const float lo = (-120.0f - neg_m) * inv_scale;
                         float2 sum_a = pk2(0.f, 0.f), sum_b = pk2(0.f, 0.f);
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
-                            const uint32_t lo = (i < 16) ? r0[2 * i] : r1[2 * (i - 16)];
-                            const uint32_t hi = (i < 16) ? r0[2 * i + 1] : r1[2 * (i - 16) + 1];
-                            const float2 x2 = fma2(pk2(__uint_as_float(lo), __uint_as_float(hi)), scale2, negm2);
+                            const float s0 = __uint_as_float((i < 16) ? r0[2 * i] : r1[2 * (i - 16)]);
+                            const float s1 = __uint_as_float((i < 16) ? r0[2 * i + 1] : r1[2 * (i - 16) + 1]);
                             float e0, e1;
-                            if ((i & 7) < A_POLY_PAIRS) {
-                                exp2_poly_pair(x2, e0, e1);
+                            if (((i * A_POLY_PAIRS) & 7) < A_POLY_PAIRS) {         // A_POLY_PAIRS of every 8 pairs, evenly spread
+                                exp2_poly_pair(s0, s1, lo, scale2, mm2, e0, e1);
                             } else {
                                 float x0, x1;
-                                upk2(x2, x0, x1);
+                                upk2(fma2(pk2(s0, s1), scale2, negm2), x0, x1);
                                 e0 = fast_exp2(x0);
                                 e1 = fast_exp2(x1);
                             }

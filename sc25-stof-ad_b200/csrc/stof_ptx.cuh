@@ -269,31 +269,25 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
-// 2^x for a pair on the FMA pipe (no MUFU): round-to-nearest split x = n + f with f in [-0.5, 0.5] by the
-// 1.5 * 2^23 magic add, degree-3 minimax polynomial for 2^f (max relative error 7.5e-5, far below the
-// 4.9e-4 quantisation of the fp16 value it feeds), exponent inserted with an integer shift-add.
-// Inputs below -126 are clamped (the result is then ~1e-38 instead of 0).
-__device__ __forceinline__ void exp2_poly_pair(float2 x2, float& e0, float& e1) {
-    float x0, x1;
-    upk2(x2, x0, x1);
-    x0 = fmaxf(x0, -126.0f);
-    x1 = fmaxf(x1, -126.0f);
-    const float2 xc = pk2(x0, x1);
-    const float2 magic = pk2(12582912.0f, 12582912.0f);
-    const float2 xf = add2(xc, magic);
-    const float2 fr = add2(xc, fma2(xf, pk2(-1.0f, -1.0f), magic));      // x - round(x): magic - xf is exact
+// 2^(s * scale - m) for a pair of raw scores on the FMA pipe (no MUFU).  `mm` = 1.5 * 2^23 - m with m an INTEGER (so mm is
+// exact): t = s * scale + mm rounds x = s * scale - m to the nearest integer n in its low mantissa bits, mm - t = -(m + n) is
+// exact, and the fraction f = s * scale - (m + n) in [-0.5, 0.5] comes out of one more FMA.  Degree-3 minimax polynomial for
+// 2^f (max relative error 7.5e-5, far below the 4.9e-4 quantisation of the fp16 value it feeds); the exponent is inserted
+// with a shift-add on the integer pipe.  Scores are clamped from below at `lo` (the score at which x = -120; the result is
+// then ~1e-36 instead of 0), which also covers -inf.
+__device__ __forceinline__ void exp2_poly_pair(float s0, float s1, float lo, float2 scale2, float2 mm2, float& e0, float& e1) {
+    const float2 sc = pk2(fmaxf(s0, lo), fmaxf(s1, lo));
+    const float2 t = fma2(sc, scale2, mm2);
+    const float2 d = fma2(t, pk2(-1.0f, -1.0f), mm2);
+    const float2 fr = fma2(sc, scale2, d);
     float2 p = fma2(pk2(0.0551716685295105f, 0.0551716685295105f), fr, pk2(0.2426111251115799f, 0.2426111251115799f));
     p = fma2(p, fr, pk2(0.6932609677314758f, 0.6932609677314758f));
     p = fma2(p, fr, pk2(0.9999280571937561f, 0.9999280571937561f));
-    float p0, p1, f0, f1;
+    float p0, p1, t0, t1;
     upk2(p, p0, p1);
-    upk2(xf, f0, f1);
-    // bits(p) + (n << 23) as one integer multiply-add (FMA pipe) per element
-    int i0, i1;
-    asm("mad.lo.s32 %0, %1, 8388608, %2;" : "=r"(i0) : "r"(__float_as_int(f0)), "r"(__float_as_int(p0)));
-    asm("mad.lo.s32 %0, %1, 8388608, %2;" : "=r"(i1) : "r"(__float_as_int(f1)), "r"(__float_as_int(p1)));
-    e0 = __int_as_float(i0);
-    e1 = __int_as_float(i1);
+    upk2(t, t0, t1);
+    e0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
+    e1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
 }
 
 }  // namespace stof
