@@ -84,3 +84,90 @@ def block_attn_mask(q, k, v, full_row_ptr, full_col_idx, part_row_ptr, part_col_
         raise _lib.StofError("block_attn_mask: q must be contiguous (it is overwritten in place)")
     return block_attention(q, k.contiguous(), v.contiguous(), q, full_row_ptr, full_col_idx, part_row_ptr, part_col_idx,
                            part_block_mask.contiguous(), load_row_ptr, load_col_idx, BLOCK_M, BLOCK_N, num_warps)
+
+
+class HostAttentionPipeline:
+    """Block-masked attention for q, k, v that live in (pinned) HOST memory: the batch is cut into chunks that go
+    through three CUDA streams - host-to-device copies of chunk c+1, the attention kernel on chunk c and the
+    device-to-host copy of the result of chunk c-1 run at the same time, so that a call costs about the larger
+    of the two PCIe directions instead of their sum plus the kernel.  Device staging (`slots` chunks of q, k, v;
+    the output overwrites the q slot, as the reference operator does) is allocated once and reused by later calls
+    of the same shape."""
+
+    def __init__(self, device, chunk_batch: int = 2, slots: int = 3):
+        self.device = torch.device(device)
+        self.chunk = int(chunk_batch)
+        self.slots = int(slots)
+        self._shape = None
+        self._stage = None
+        self._s_in = torch.cuda.Stream(self.device)
+        self._s_run = torch.cuda.Stream(self.device)
+        self._s_out = torch.cuda.Stream(self.device)
+
+    def _staging(self, heads, seq_len, head_dim):
+        shape = (self.chunk, heads, seq_len, head_dim)
+        if self._shape != shape:
+            self._stage = [tuple(torch.empty(shape, dtype=torch.float16, device=self.device) for _ in range(3)) for _ in range(self.slots)]
+            self._shape = shape
+        return self._stage
+
+    def __call__(self, q_host, k_host, v_host, out_host, full_row_ptr, full_col_idx, part_row_ptr, part_col_idx, part_block_mask,
+                 load_row_ptr, load_col_idx, block_m: int, block_n: int, num_warps: int = 4):
+        for t in (q_host, k_host, v_host, out_host):
+            if t.device.type != "cpu" or t.dtype != torch.float16 or not t.is_contiguous():
+                raise _lib.StofError("host attention: q, k, v and out must be contiguous float16 CPU tensors (pinned for overlap)")
+        B, H, S, D = q_host.shape
+        if k_host.shape != q_host.shape or v_host.shape != q_host.shape or out_host.shape != q_host.shape:
+            raise _lib.StofError("host attention: q, k, v and out must share one (B,H,S,D) shape")
+        stage = self._staging(H, S, D)
+        cur = torch.cuda.current_stream(self.device)
+        start = torch.cuda.Event()
+        start.record(cur)
+        for st in (self._s_in, self._s_run, self._s_out):
+            st.wait_event(start)                       # everything enqueued before the call comes first
+        slot_free = [None] * self.slots
+        last = None
+        for c, b0 in enumerate(range(0, B, self.chunk)):
+            nb = min(self.chunk, B - b0)
+            qd, kd, vd = (t[:nb] for t in stage[c % self.slots])
+            with torch.cuda.stream(self._s_in):
+                if slot_free[c % self.slots] is not None:
+                    self._s_in.wait_event(slot_free[c % self.slots])      # the slot's previous result has left the device
+                qd.copy_(q_host[b0:b0 + nb], non_blocking=True)
+                kd.copy_(k_host[b0:b0 + nb], non_blocking=True)
+                vd.copy_(v_host[b0:b0 + nb], non_blocking=True)
+                loaded = torch.cuda.Event()
+                loaded.record(self._s_in)
+            with torch.cuda.stream(self._s_run):
+                self._s_run.wait_event(loaded)
+                block_attention(qd, kd, vd, qd, full_row_ptr, full_col_idx, part_row_ptr, part_col_idx, part_block_mask,
+                                load_row_ptr, load_col_idx, block_m, block_n, num_warps)
+                computed = torch.cuda.Event()
+                computed.record(self._s_run)
+            with torch.cuda.stream(self._s_out):
+                self._s_out.wait_event(computed)
+                out_host[b0:b0 + nb].copy_(qd, non_blocking=True)
+                done = torch.cuda.Event()
+                done.record(self._s_out)
+            slot_free[c % self.slots] = done
+            last = done
+        if last is not None:
+            cur.wait_event(last)                       # the caller's stream sees the whole result (copies leave in order)
+        return out_host
+
+
+_HOST_PIPELINES = {}
+
+
+def block_attention_host(q_host, k_host, v_host, out_host, full_row_ptr, full_col_idx, part_row_ptr, part_col_idx, part_block_mask,
+                         load_row_ptr, load_col_idx, block_m: int, block_n: int, num_warps: int = 4, chunk_batch: int = 2):
+    """`block_attn_mask` for host-resident q, k, v: result in `out_host` (may be `q_host`), copies overlapped with
+    the kernel by a per-device `HostAttentionPipeline`.  The block index tensors are device tensors, as for the
+    device-side operator (src/ops/package_op.py:50-74)."""
+    dev = full_row_ptr.device
+    key = (str(dev), int(chunk_batch))
+    pipe = _HOST_PIPELINES.get(key)
+    if pipe is None:
+        pipe = _HOST_PIPELINES[key] = HostAttentionPipeline(dev, chunk_batch)
+    return pipe(q_host, k_host, v_host, out_host, full_row_ptr, full_col_idx, part_row_ptr, part_col_idx, part_block_mask,
+                load_row_ptr, load_col_idx, block_m, block_n, num_warps)
