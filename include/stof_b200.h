@@ -132,13 +132,15 @@ int stof_block_attn(const void* q, const void* k, const void* v, void* out,
  *
  * A row-major with row stride lda, W row-major (K rows) with row stride ldw, C row-major with row
  * stride ldc; all in elements, multiples of 8; pointers 16-byte aligned; K, N multiples of 8.
- * epilogue: STOF_EPI_BIAS, _GELU_ERF, _GELU_TANH, _RESIDUAL (adds residual[M,N], row stride ldr).
+ * epilogue: STOF_EPI_BIAS, _GELU_ERF, _GELU_TANH, _RESIDUAL (adds residual[M,N], row stride ldr), _RELU
+ * (max(x, 0): the FFN activation of the T5 loops, src/benchmk_end2end.py:203,313).
  * bias may be NULL.
  * ------------------------------------------------------------------------------------------ */
 #define STOF_EPI_BIAS 0
 #define STOF_EPI_BIAS_GELU_ERF 1
 #define STOF_EPI_BIAS_GELU_TANH 2
 #define STOF_EPI_BIAS_RESIDUAL 3
+#define STOF_EPI_BIAS_RELU 4
 
 int stof_gemm_bias_act(const void* a, long long lda, const void* w, long long ldw, const void* bias,
                        const void* residual, long long ldr, void* c, long long ldc,

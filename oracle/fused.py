@@ -88,9 +88,69 @@ def bert_layer(hidden, params: dict, mask, head_num: int, eps: float = 1e-5, qkv
     y = torch.matmul(h, params["Wo"].float()) + params["bo"].float() + x
     y = F.layer_norm(y, (hid,), params["g1"].float(), params["b1"].float(), eps)
     z = torch.matmul(y, params["W1"].float()) + params["bi1"].float()
-    z = F.gelu(z) if gelu_mode == "erf" else gelu_tanh(z)
+    z = _activation(z, gelu_mode)
     z = torch.matmul(z, params["W2"].float()) + params["bi2"].float() + y
     return F.layer_norm(z, (hid,), params["g2"].float(), params["b2"].float(), eps)
+
+
+def _activation(z: torch.Tensor, mode: str) -> torch.Tensor:
+    """FFN activation of the three model loops: "erf" = F.gelu (BERT, src/benchmk_end2end.py:81), "tanh" = `new_gelu`
+    (GPT-2, :142), "relu" = F.relu (T5, :203 and :313)."""
+    if mode == "erf":
+        return F.gelu(z)
+    if mode == "tanh":
+        return gelu_tanh(z)
+    if mode == "relu":
+        return F.relu(z)
+    raise ValueError(mode)
+
+
+def _attention_fp32(x, Wqkv, bqkv, mask, head_num: int) -> torch.Tensor:
+    """QKV projection + the reference's torch-native attention branch (src/benchmk_end2end.py:44-52), merged heads."""
+    B, S, hid = x.shape
+    hs = hid // head_num
+    qkv = torch.matmul(x, Wqkv.float()) + bqkv.float()
+    q, k, v = (t.reshape(B, S, head_num, hs).permute(0, 2, 1, 3) for t in qkv.chunk(3, dim=-1))
+    scores = torch.matmul(q, k.transpose(-2, -1)) / (hs ** .5)
+    scores = scores - 10000.0 * (1.0 - torch.as_tensor(mask).float().unsqueeze(1))
+    return torch.matmul(F.softmax(scores, dim=-1), v).permute(0, 2, 1, 3).reshape(B, S, hid)
+
+
+def t5_decoder_layer(hidden, params: dict, mask, head_num: int, eps: float = 1e-5) -> torch.Tensor:
+    """One decoder layer of the reference's T5 loop (src/benchmk_end2end.py:230-316) in fp32: masked self-attention,
+    out-projection + residual + LayerNorm, a second attention sublayer whose Q, K and V all come from the decoder state
+    (the loop projects `decoder_hidden_states` with `qkv_kernel_3`, :263-268), out-projection + residual + LayerNorm,
+    and the ReLU feed-forward + residual + LayerNorm.  The first sublayer's QKV is projected from the layer input here
+    (the script feeds a ready activation in place of that GEMM, :232).
+
+    params: Wqkv_a, bqkv_a, Wo_a, bo_a, g_a, b_a (first attention), Wqkv_c, bqkv_c, Wo_c, bo_c, g_c, b_c (second),
+    W1, bi1, W2, bi2, g2, b2 (feed-forward)."""
+    x = hidden.float()
+    hid = x.shape[-1]
+    f = lambda k: params[k].float()
+    h = _attention_fp32(x, params["Wqkv_a"], params["bqkv_a"], mask, head_num)
+    y = F.layer_norm(torch.matmul(h, f("Wo_a")) + f("bo_a") + x, (hid,), f("g_a"), f("b_a"), eps)
+    h = _attention_fp32(y, params["Wqkv_c"], params["bqkv_c"], mask, head_num)
+    y2 = F.layer_norm(torch.matmul(h, f("Wo_c")) + f("bo_c") + y, (hid,), f("g_c"), f("b_c"), eps)
+    z = F.relu(torch.matmul(y2, f("W1")) + f("bi1"))
+    z = torch.matmul(z, f("W2")) + f("bi2") + y2
+    return F.layer_norm(z, (hid,), f("g2"), f("b2"), eps)
+
+
+def make_t5_decoder_params(hidden: int, ffn: int, seed: int, dtype=torch.float16):
+    """Seeded CPU weights of one decoder layer: W ~ N(0, 0.02), biases and affine terms uniform(-0.4, 0.4) around 0 / 1
+    (src/benchmk_end2end.py:453-454).  Draw order = the order of the `params` list in `t5_decoder_layer`."""
+    g = torch.Generator().manual_seed(seed)
+    w = lambda *shape: (torch.randn(*shape, generator=g) * 0.02).to(dtype)
+    u = lambda n, base: (base + (torch.rand(n, generator=g) * 0.8 - 0.4) * 0.25).to(dtype)
+    p = {}
+    for tag in ("a", "c"):
+        p["Wqkv_" + tag] = w(hidden, 3 * hidden); p["bqkv_" + tag] = u(3 * hidden, 0.0)
+        p["Wo_" + tag] = w(hidden, hidden); p["bo_" + tag] = u(hidden, 0.0)
+        p["g_" + tag] = u(hidden, 1.0); p["b_" + tag] = u(hidden, 0.0)
+    p["W1"] = w(hidden, ffn); p["bi1"] = u(ffn, 0.0); p["W2"] = w(ffn, hidden); p["bi2"] = u(hidden, 0.0)
+    p["g2"] = u(hidden, 1.0); p["b2"] = u(hidden, 0.0)
+    return p
 
 
 def make_bert_params(hidden: int, ffn: int, layers: int, seed: int, dtype=torch.float16, random_affine: bool = False):

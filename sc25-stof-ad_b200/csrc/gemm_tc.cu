@@ -222,6 +222,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                             } else if (EPI == STOF_EPI_BIAS_GELU_TANH) {
 #pragma unroll
                                 for (int j = 0; j < 4; ++j) v[j] = gelu_tanh2(v[j]);
+                            } else if (EPI == STOF_EPI_BIAS_RELU) {
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    float x0, x1;
+                                    upk2(v[j], x0, x1);
+                                    v[j] = pk2(fmaxf(x0, 0.0f), fmaxf(x1, 0.0f));
+                                }
                             } else if (EPI == STOF_EPI_BIAS_RESIDUAL) {
                                 const __half2* rh = reinterpret_cast<const __half2*>(&res[ch][g]);
 #pragma unroll
@@ -291,7 +298,7 @@ extern "C" int stof_gemm_bias_act(const void* a, long long lda, const void* w, l
     STOF_REQUIRE(lda % 8 == 0 && ldw % 8 == 0 && ldc % 8 == 0, "gemm: leading dimensions must be multiples of 8 elements");
     STOF_REQUIRE(lda >= k && ldw >= n && ldc >= n, "gemm: leading dimension smaller than the row length");
     STOF_REQUIRE(aligned16(a) && aligned16(w) && aligned16(c) && aligned16(bias) && aligned16(residual), "gemm: pointers must be 16-byte aligned");
-    STOF_REQUIRE(epilogue >= STOF_EPI_BIAS && epilogue <= STOF_EPI_BIAS_RESIDUAL, "gemm: unknown epilogue %d", epilogue);
+    STOF_REQUIRE(epilogue >= STOF_EPI_BIAS && epilogue <= STOF_EPI_BIAS_RELU, "gemm: unknown epilogue %d", epilogue);
     if (epilogue == STOF_EPI_BIAS_RESIDUAL)
         STOF_REQUIRE(residual && ldr % 8 == 0 && ldr >= n, "gemm: residual epilogue needs a residual with a row stride multiple of 8, >= n");
     if (m == 0) return STOF_OK;
@@ -321,6 +328,7 @@ extern "C" int stof_gemm_bias_act(const void* a, long long lda, const void* w, l
         case STOF_EPI_BIAS: return launch<STOF_EPI_BIAS>(ma, mw, mc, bp, rp, ldr, m, n, k, status_dev, stream);
         case STOF_EPI_BIAS_GELU_ERF: return launch<STOF_EPI_BIAS_GELU_ERF>(ma, mw, mc, bp, rp, ldr, m, n, k, status_dev, stream);
         case STOF_EPI_BIAS_GELU_TANH: return launch<STOF_EPI_BIAS_GELU_TANH>(ma, mw, mc, bp, rp, ldr, m, n, k, status_dev, stream);
+        case STOF_EPI_BIAS_RELU: return launch<STOF_EPI_BIAS_RELU>(ma, mw, mc, bp, rp, ldr, m, n, k, status_dev, stream);
         default: return launch<STOF_EPI_BIAS_RESIDUAL>(ma, mw, mc, bp, rp, ldr, m, n, k, status_dev, stream);
     }
 }

@@ -9,7 +9,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.environ.get("STOF_B200_LIBRARY") or os.path.join(_HERE, "libstof_b200.so")
 
 STOF_DTYPE_F16, STOF_DTYPE_F32 = 0, 1
-EPI_BIAS, EPI_BIAS_GELU_ERF, EPI_BIAS_GELU_TANH, EPI_BIAS_RESIDUAL = 0, 1, 2, 3
+EPI_BIAS, EPI_BIAS_GELU_ERF, EPI_BIAS_GELU_TANH, EPI_BIAS_RESIDUAL, EPI_BIAS_RELU = 0, 1, 2, 3, 4
 
 EXPORTS = ("stof_version", "stof_last_error", "stof_mask_workspace_bytes", "stof_mask_classify", "stof_mask_fill", "stof_mask_compact_static",
            "stof_block_attn_plan_bytes", "stof_block_attn_plan", "stof_block_attn", "stof_gemm_bias_act", "stof_bias_residual_layernorm")

@@ -1,5 +1,6 @@
-"""Post-LN BERT encoder forward built from the fused operators
-(reference loop: src/benchmk_end2end.py:31-88, QKV projection as in src/model-candidate/1-BERT-large.py:17-18)."""
+"""Post-LN transformer forward passes built from the fused operators: the BERT encoder (reference loop:
+src/benchmk_end2end.py:31-88, QKV projection as in src/model-candidate/1-BERT-large.py:17-18), its GPT-2 and T5-encoder
+variants (same loop with the tanh GELU, :93-147, or ReLU, :152-208) and the T5 decoder layer (:230-316)."""
 from __future__ import annotations
 
 from dataclasses import dataclass
@@ -9,7 +10,7 @@ import torch
 
 from . import _lib
 from .attention import block_attention
-from .fused import bias_residual_layernorm, gemm_bias, gemm_bias_gelu, gemm_bias_residual
+from .fused import bias_residual_layernorm, gemm_bias, gemm_bias_act, gemm_bias_residual
 from .masks import get_sparse_storage
 
 
@@ -43,6 +44,9 @@ class BertEncoder:
 
     def __init__(self, layers: List[EncoderWeights], head_num: int, eps: float = 1e-12, gelu: str = "erf",
                  block_m: int = 64, block_n: int = 64):
+        """`gelu` names the feed-forward activation: "erf" (BERT), "tanh" (GPT-2 `new_gelu`) or "relu" (T5)."""
+        if gelu not in ("erf", "tanh", "relu"):
+            raise _lib.StofError(f"encoder: unknown activation {gelu!r}")
         self.layers = layers
         self.head_num = head_num
         self.eps = eps
@@ -92,9 +96,94 @@ class BertEncoder:
             y = y_bufs[yi]; yi = (yi + 1) % 3
             gemm_bias_residual(ctx, w.Wo, w.bo, x, out=y)
             bias_residual_layernorm(y, None, None, w.g1, w.b1, self.eps, out=y)
-            gemm_bias_gelu(y, w.W1, w.bi1, self.gelu, out=inter)
+            gemm_bias_act(y, w.W1, w.bi1, self.gelu, out=inter)
             z = y_bufs[yi]; yi = (yi + 1) % 3
             gemm_bias_residual(inter, w.W2, w.bi2, y, out=z)
+            bias_residual_layernorm(z, None, None, w.g2, w.b2, self.eps, out=z)
+            x = z
+        return x
+
+    __call__ = forward
+
+
+def gpt2_stack(layers: List[EncoderWeights], head_num: int, eps: float = 1e-5, block_m: int = 64, block_n: int = 64) -> BertEncoder:
+    """The reference's GPT-2 loop (src/benchmk_end2end.py:93-147): the same post-LN layer with the tanh-form GELU;
+    the caller sets a causal mask."""
+    return BertEncoder(layers, head_num, eps, "tanh", block_m, block_n)
+
+
+def t5_encoder_stack(layers: List[EncoderWeights], head_num: int, eps: float = 1e-5, block_m: int = 64, block_n: int = 64) -> BertEncoder:
+    """The encoder half of the reference's T5 loop (src/benchmk_end2end.py:152-208): the same layer with ReLU."""
+    return BertEncoder(layers, head_num, eps, "relu", block_m, block_n)
+
+
+@dataclass
+class T5DecoderWeights:
+    """One decoder layer: two attention sublayers (suffix _a, _c: Wqkv, bqkv, Wo, bo, g, b) and the feed-forward
+    (W1, bi1, W2, bi2, g2, b2)."""
+    Wqkv_a: torch.Tensor
+    bqkv_a: torch.Tensor
+    Wo_a: torch.Tensor
+    bo_a: torch.Tensor
+    g_a: torch.Tensor
+    b_a: torch.Tensor
+    Wqkv_c: torch.Tensor
+    bqkv_c: torch.Tensor
+    Wo_c: torch.Tensor
+    bo_c: torch.Tensor
+    g_c: torch.Tensor
+    b_c: torch.Tensor
+    W1: torch.Tensor
+    bi1: torch.Tensor
+    W2: torch.Tensor
+    bi2: torch.Tensor
+    g2: torch.Tensor
+    b2: torch.Tensor
+
+    @staticmethod
+    def from_dict(p: dict, device) -> "T5DecoderWeights":
+        names = [f.name for f in T5DecoderWeights.__dataclass_fields__.values()]
+        return T5DecoderWeights(**{k: p[k].to(device=device, dtype=torch.float16).contiguous() for k in names})
+
+
+class T5Decoder(BertEncoder):
+    """Decoder layers of the reference's T5 loop (src/benchmk_end2end.py:230-316): masked self-attention, a second
+    attention sublayer on the decoder state, and the ReLU feed-forward, each followed by residual + LayerNorm.  Per layer
+    ten kernel launches (3 QKV/out-proj GEMM pairs and FFN GEMMs with fused epilogues, 2 attentions, 3 LayerNorms)."""
+
+    def __init__(self, layers: List[T5DecoderWeights], head_num: int, eps: float = 1e-5, block_m: int = 64, block_n: int = 64):
+        super().__init__(layers, head_num, eps, "relu", block_m, block_n)
+
+    def forward(self, hidden: torch.Tensor) -> torch.Tensor:
+        if self._index is None:
+            raise _lib.StofError("T5Decoder: call set_mask() or set_index() first")
+        B, S, hid = hidden.shape
+        H = self.head_num
+        D = hid // H
+        dev = hidden.device
+        frp, fci, prp, pci, pbm, lrp, lci = self._index
+        qkv = self._buf("qkv", (B, S, 3 * hid), dev)
+        ctx = self._buf("ctx", (B, S, hid), dev)
+        inter = self._buf("inter", (B, S, self.layers[0].W1.shape[1]), dev)
+        ys = [self._buf(f"y{i}", (B, S, hid), dev) for i in range(4)]
+        yi = 0
+
+        def attention_sublayer(x, Wqkv, bqkv, Wo, bo, g, b, out):
+            gemm_bias(x, Wqkv, bqkv, out=qkv)
+            q5 = qkv.view(B, S, 3, H, D)
+            q, k, v = (q5[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+            block_attention(q, k, v, ctx.view(B, S, H, D).permute(0, 2, 1, 3), frp, fci, prp, pci, pbm, lrp, lci, self.block_m, self.block_n)
+            gemm_bias_residual(ctx, Wo, bo, x, out=out)
+            bias_residual_layernorm(out, None, None, g, b, self.eps, out=out)
+            return out
+
+        x = hidden
+        for w in self.layers:
+            y = attention_sublayer(x, w.Wqkv_a, w.bqkv_a, w.Wo_a, w.bo_a, w.g_a, w.b_a, ys[yi]); yi = (yi + 1) % 4
+            y2 = attention_sublayer(y, w.Wqkv_c, w.bqkv_c, w.Wo_c, w.bo_c, w.g_c, w.b_c, ys[yi]); yi = (yi + 1) % 4
+            gemm_bias_act(y2, w.W1, w.bi1, "relu", out=inter)
+            z = ys[yi]; yi = (yi + 1) % 4
+            gemm_bias_residual(inter, w.W2, w.bi2, y2, out=z)
             bias_residual_layernorm(z, None, None, w.g2, w.b2, self.eps, out=z)
             x = z
         return x

@@ -68,6 +68,20 @@ def gemm_bias_gelu(a, w, bias=None, mode: str = "erf", out=None):
     return _gemm(a, w, bias, _lib.EPI_BIAS_GELU_ERF if mode == "erf" else _lib.EPI_BIAS_GELU_TANH, out=out)
 
 
+def gemm_bias_relu(a, w, bias=None, out=None):
+    """GEMM + bias + ReLU in one kernel (the FFN activation of the T5 loops, src/benchmk_end2end.py:203,313)."""
+    return _gemm(a, w, bias, _lib.EPI_BIAS_RELU, out=out)
+
+
+def gemm_bias_act(a, w, bias=None, activation: str = "gelu_erf", out=None):
+    """GEMM + bias + activation by name: "gelu_erf" (BERT), "gelu_tanh" (GPT-2 `new_gelu`), "relu" (T5), "none"."""
+    epi = {"gelu_erf": _lib.EPI_BIAS_GELU_ERF, "erf": _lib.EPI_BIAS_GELU_ERF, "gelu_tanh": _lib.EPI_BIAS_GELU_TANH,
+           "tanh": _lib.EPI_BIAS_GELU_TANH, "relu": _lib.EPI_BIAS_RELU, "none": _lib.EPI_BIAS}.get(activation)
+    if epi is None:
+        raise _lib.StofError(f"gemm_bias_act: unknown activation {activation!r}")
+    return _gemm(a, w, bias, epi, out=out)
+
+
 def gemm_bias_residual(a, w, bias, residual, out=None):
     """GEMM + bias + residual add in one kernel."""
     return _gemm(a, w, bias, _lib.EPI_BIAS_RESIDUAL, residual=residual, out=out)

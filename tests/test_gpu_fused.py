@@ -136,3 +136,44 @@ def test_two_layer_encoder_random_affine():
     assert _err(got, want) <= 3e-3 * max(1.0, want.abs().max().item())     # two layers of fp16 storage
     again = enc(hidden.cuda())
     assert torch.equal(again, got)                                          # deterministic, buffers reused
+
+
+def test_gemm_bias_relu():
+    import stof_b200
+    a, w, b = _rand((300, 200), 5), _rand((200, 264), 6, 0.1), _rand((264,), 7)
+    got = stof_b200.gemm_bias_relu(a.cuda(), w.cuda(), b.cuda())
+    want = torch.relu(of.gemm_bias(a, w, b))
+    assert _err(got, want) <= 2e-3 * max(1.0, want.abs().max().item())
+    assert (got >= 0).all()
+
+
+@pytest.mark.parametrize("activation", ["tanh", "relu"])
+def test_gpt2_and_t5_encoder_layers(activation):
+    """The GPT-2 loop (tanh GELU, causal mask) and the T5 encoder loop (ReLU) are the BERT layer with another activation."""
+    import stof_b200
+    B, S, hid, heads, ffn = 2, 256, 256, 4, 1024
+    params = of.make_bert_params(hid, ffn, 2, seed=21, random_affine=True)
+    hidden = _rand((B, S, hid), 22)
+    mask = om.generate_causal_mask(1, S).astype(np.float16) if activation == "tanh" else om.generate_sliding_mask(1, S, 40, False, np.float16)
+    make = stof_b200.gpt2_stack if activation == "tanh" else stof_b200.t5_encoder_stack
+    model = make([stof_b200.EncoderWeights.from_dict(p, "cuda") for p in params], heads, 1e-5, 32, 32)
+    model.set_mask(torch.from_numpy(mask).cuda())
+    got = model(hidden.cuda())
+    torch.cuda.synchronize()
+    want = of.encoder_forward(hidden, params, torch.from_numpy(mask.astype(np.float32)), heads, 1e-5, activation)
+    assert _err(got, want) <= 3e-3 * max(1.0, want.abs().max().item())
+
+
+def test_t5_decoder_layer():
+    """Two attention sublayers + ReLU feed-forward (the decoder loop of the reference's T5 forward) on a causal mask."""
+    import stof_b200
+    B, S, hid, heads, ffn = 2, 256, 256, 4, 512
+    params = of.make_t5_decoder_params(hid, ffn, seed=31)
+    hidden = _rand((B, S, hid), 32)
+    mask = om.generate_causal_mask(1, S).astype(np.float16)
+    dec = stof_b200.T5Decoder([stof_b200.T5DecoderWeights.from_dict(params, "cuda")], heads, 1e-5, 32, 32)
+    dec.set_mask(torch.from_numpy(mask).cuda())
+    got = dec(hidden.cuda())
+    torch.cuda.synchronize()
+    want = of.t5_decoder_layer(hidden, params, torch.from_numpy(mask.astype(np.float32)), heads, 1e-5)
+    assert _err(got, want) <= 3e-3 * max(1.0, want.abs().max().item())
