@@ -178,6 +178,37 @@ def run_attention(args, rank, world, local):
         comp_ms.append(ev0.elapsed_time(ev1))
     nnz, frp, fci, prp, pci, pbm, lrp, lci = idx
     n_load = int(lrp[-1].item())
+    # the two compaction kernels alone (sizes known, no host read in between): enqueued back to back, and as a CUDA graph replay
+    refresher = stof_b200.SparseStorageRefresher(mask, cfg.block, cfg.block)
+    reps = 50
+    for _ in range(5):
+        refresher.refresh()
+    torch.cuda.synchronize(dev)
+    ev0.record()
+    for _ in range(reps):
+        refresher.refresh()
+    ev1.record()
+    torch.cuda.synchronize(dev)
+    comp_eager_us = ev0.elapsed_time(ev1) / reps * 1e3
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):
+        refresher.refresh()
+    torch.cuda.current_stream(dev).wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        refresher.refresh()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize(dev)
+    ev0.record()
+    for _ in range(reps):
+        graph.replay()
+    ev1.record()
+    torch.cuda.synchronize(dev)
+    comp_graph_us = ev0.elapsed_time(ev1) / reps * 1e3
+    refresher.check()
+    del graph
     flops = wl.attention_flops(n_load, cfg.batch, cfg.heads, cfg.block, cfg.block, cfg.head_dim)
 
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
@@ -281,7 +312,9 @@ def run_attention(args, rank, world, local):
         "gpu_launches": args.steps,
         "clocks": clocks.summary(),
         "compaction": {"ms": comp_best, "mask_bytes": mask_bytes, "gbs": mask_bytes / (comp_best * 1e-3) / 1e9,
-                       "note": "classify + fill + host read of the three totals, S=%d" % cfg.seq_len},
+                       "note": "classify + fill + host read of the three totals, S=%d" % cfg.seq_len,
+                       "kernels_back_to_back_us": comp_eager_us, "kernels_graph_replay_us": comp_graph_us,
+                       "kernels_gbs": mask_bytes / (comp_graph_us * 1e-6) / 1e9},
         "wall_s_timed_region": wall, "output_finite": finite,
     }
     if encoder is not None:

@@ -139,15 +139,32 @@ classify_kernel(const void* __restrict__ mask, int seq_len, int bm, int bn, int 
     const int chunks_per_row = cols / EPC;
     const int total = bm * chunks_per_row;
     unsigned nz = 0;
-    for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
-        const int r = idx / chunks_per_row, cc = idx - r * chunks_per_row;
-        const uint4 v = __ldg(reinterpret_cast<const uint4*>(base + (static_cast<size_t>(r) * seq_len + cc * EPC) * elem_bytes));
-        unsigned f = 0;
-        chunk_flags<F32>(v, f, nz);
-        if (batch == 0 && f) {
-            const int t = (cc * EPC) / bn;
-            // several threads may set the same bits; every writer ORs in bits that stay set
-            if ((s_flags[t] & f) != f) atomicOr(reinterpret_cast<unsigned int*>(&s_flags[t & ~3]), f << (8 * (t & 3)));
+    // four independent 16-byte loads in flight per thread before any of them is consumed
+    constexpr int BATCH = 4;
+    for (int idx0 = threadIdx.x; idx0 < total; idx0 += BATCH * blockDim.x) {
+        uint4 v[BATCH];
+        int tile_of[BATCH];
+#pragma unroll
+        for (int u = 0; u < BATCH; ++u) {
+            const int idx = idx0 + u * blockDim.x;
+            if (idx < total) {
+                const int r = idx / chunks_per_row, cc = idx - r * chunks_per_row;
+                v[u] = __ldg(reinterpret_cast<const uint4*>(base + (static_cast<size_t>(r) * seq_len + cc * EPC) * elem_bytes));
+                tile_of[u] = (cc * EPC) / bn;
+            } else {
+                tile_of[u] = -1;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < BATCH; ++u) {
+            if (tile_of[u] < 0) continue;
+            unsigned f = 0;
+            chunk_flags<F32>(v[u], f, nz);
+            if (batch == 0 && f) {
+                const int t = tile_of[u];
+                // several threads may set the same bits; every writer ORs in bits that stay set
+                if ((s_flags[t] & f) != f) atomicOr(reinterpret_cast<unsigned int*>(&s_flags[t & ~3]), f << (8 * (t & 3)));
+            }
         }
     }
 #pragma unroll
@@ -377,9 +394,9 @@ extern "C" int stof_mask_classify(const void* mask, int mask_dtype, int batch, i
     }
     const int nbm = seq_len / block_m;
     STOF_REQUIRE(nbm <= 65535, "mask_classify: more than 65535 block rows");
-    // stripe width: whole tiles, at least 256 columns for coalescing, enough stripes to fill the GPU
+    // stripe width: whole tiles, at least 128 columns (256-byte row segments) for coalescing, enough stripes to fill the GPU
     int unit = block_n;
-    while (unit < 256 && unit < seq_len) unit += block_n;
+    while (unit < 128 && unit < seq_len) unit += block_n;
     const int units = (seq_len + unit - 1) / unit;
     int want = (4 * sm_count() + nbm * batch - 1) / (nbm * batch);
     if (want < 1) want = 1;
@@ -459,7 +476,7 @@ extern "C" int stof_mask_compact_static(const void* mask, int mask_dtype, int ba
     unsigned char* cls = scratch + WS_HEADER;
 
     int unit = block_n;
-    while (unit < 256 && unit < seq_len) unit += block_n;
+    while (unit < 128 && unit < seq_len) unit += block_n;
     const int units = (seq_len + unit - 1) / unit;
     int want = (4 * sm_count() + nbm * batch - 1) / (nbm * batch);
     if (want < 1) want = 1;

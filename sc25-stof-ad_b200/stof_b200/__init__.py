@@ -7,7 +7,7 @@ fallback: if the shared library is missing or a tensor is not on a CUDA device t
 be used, the call raises.
 """
 from ._lib import StofError, lib, library_path  # noqa: F401
-from .masks import (get_sparse_storage, generate_causal_mask, generate_sliding_mask, generate_dilated_mask,  # noqa: F401
+from .masks import (get_sparse_storage, SparseStorageRefresher, generate_causal_mask, generate_sliding_mask, generate_dilated_mask,  # noqa: F401
                     generate_longformer_mask, generate_bigbird_mask)
 from .attention import block_attn_mask, block_attention, block_attention_host, HostAttentionPipeline  # noqa: F401
 from .rowwise import rowwise_attn_full, rowwise_attn_sliding, rowwise_attn_mask  # noqa: F401

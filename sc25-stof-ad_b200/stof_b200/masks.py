@@ -67,6 +67,52 @@ def get_sparse_storage(Mask: torch.Tensor, block_size_m: int, block_size_n: int)
     return out
 
 
+class SparseStorageRefresher:
+    """Recomputes the block index of a mask whose NUMBER of full / partial / loaded blocks is already known (the same
+    mask structure evaluated again, e.g. every step of a serving loop) into buffers allocated once, with one call of
+    the bounded single-call compaction (`stof_mask_compact_static`): no workspace, no host read, nothing allocated.
+    `refresh()` returns the same tuple as `get_sparse_storage` (views of the buffers).  The buffers are sized for the
+    counts of the mask seen at construction; blocks beyond them are dropped on the device, never written out of bounds,
+    and `check()` (a host read) raises when the counts of the last refresh differ.  Refreshes must not overlap on the
+    GPU (they share the library's built-in scratch): keep them on one stream."""
+
+    def __init__(self, Mask: torch.Tensor, block_size_m: int, block_size_n: int):
+        if not Mask.is_cuda or Mask.dim() != 3 or not Mask.is_contiguous():
+            raise _lib.StofError("SparseStorageRefresher expects a contiguous (batch, S, S) CUDA mask")
+        first = get_sparse_storage(Mask, block_size_m, block_size_n)
+        self.mask, self.bm, self.bn = Mask, int(block_size_m), int(block_size_n)
+        dev, S = Mask.device, Mask.shape[-1]
+        n_full, n_part, n_load = first[2].numel(), first[4].numel(), first[7].numel()
+        self._sizes = (n_full, n_part, n_load)
+        self._cap = max(n_load, 1)
+        self._row_ptrs = torch.empty(3, S // self.bm + 1, dtype=torch.int32, device=dev)
+        self._cols = torch.empty(3, self._cap, dtype=torch.int32, device=dev)
+        self._tile_cap = max(n_part, 1)
+        self._tiles = torch.ones(self._tile_cap, self.bm, self.bn, dtype=torch.float16, device=dev)
+        self._counts = torch.empty(4, dtype=torch.int64, device=dev)
+        self.out = (first[0], self._row_ptrs[0], self._cols[0][:n_full], self._row_ptrs[1], self._cols[1][:n_part],
+                    self._tiles, self._row_ptrs[2], self._cols[2][:n_load])
+        self.refresh()                                    # also the library's one-time scratch lookup, outside any capture
+
+    def refresh(self):
+        m, L = self.mask, _lib.lib()
+        dt = _lib.STOF_DTYPE_F16 if m.dtype == torch.float16 else _lib.STOF_DTYPE_F32
+        with torch.cuda.device(m.device):
+            rc = L.stof_mask_compact_static(_lib.ptr(m), dt, m.shape[0], m.shape[-1], self.bm, self.bn,
+                                            _lib.ptr(self._row_ptrs[0]), _lib.ptr(self._row_ptrs[1]), _lib.ptr(self._row_ptrs[2]),
+                                            _lib.ptr(self._cols[0]), _lib.ptr(self._cols[1]), _lib.ptr(self._cols[2]), self._cap,
+                                            _lib.ptr(self._tiles), self._tile_cap if self._sizes[1] else 0,
+                                            _lib.ptr(self._counts), _lib.current_stream_ptr(m.device))
+        _lib.check(rc, "stof_mask_compact_static")
+        return self.out
+
+    def check(self):
+        """Host-side check (synchronises): the refreshed mask had the block counts the buffers were sized for."""
+        n_full, n_part, n_load, _ = self._counts.tolist()
+        if (n_full, n_part, n_load) != self._sizes:
+            raise _lib.StofError(f"mask structure changed: {n_full}/{n_part}/{n_load} full/partial/loaded blocks, buffers hold {self._sizes}")
+
+
 # ------------------------------------------------------------------------------------------
 # Generators (reference: src/util/masks.py:10-122), vectorised; same signatures and results.
 # ------------------------------------------------------------------------------------------

@@ -94,3 +94,22 @@ def test_cpu_resident_mask_round_trips_through_the_gpu():
     out = stof_b200.get_sparse_storage(mask, 32, 32)
     assert all(not t.is_cuda for t in out)
     _compare(tuple(t.cuda() if i else t for i, t in enumerate(out)), om.get_sparse_storage(mask.numpy(), 32, 32))
+
+
+@pytest.mark.gpu
+def test_refresher_reuses_buffers_and_detects_structure_change():
+    """`SparseStorageRefresher` recomputes the index without a host read; same mask -> identical tensors, a mask with
+    other block counts -> `check()` raises."""
+    import stof_b200
+    S = 512
+    m1 = torch.from_numpy(om.generate_sliding_mask(1, S, 70, False, np.float16)).cuda()
+    want = stof_b200.get_sparse_storage(m1, 64, 64)
+    ref = stof_b200.SparseStorageRefresher(m1, 64, 64)
+    got = ref.refresh()
+    ref.check()
+    for a, b in zip(got[1:], want[1:]):
+        assert torch.equal(a, b)
+    m1.copy_(torch.from_numpy(om.generate_causal_mask(1, S).astype(np.float16)).cuda())      # other structure, same buffer
+    ref.refresh()
+    with pytest.raises(stof_b200.StofError):
+        ref.check()
