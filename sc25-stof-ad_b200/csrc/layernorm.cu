@@ -1,9 +1,9 @@
 // y = LayerNorm(x + bias + residual) * gamma + beta over rows of fp16, fp32 statistics (HBM-bound).
 //
-// One warp per row, persistent over rows.  A row is read once with 128-bit loads (the next row of the warp is
-// already in flight), held in registers as fp32, reduced with warp shuffles (mean, then the centred sum of
-// squares, biased variance as src/triton_template/add_layernorm.py:33-55 and F.layer_norm do), and written once
-// with 128-bit stores.  Rows longer than 2048 elements are re-read from cache for the second and third sweep
+// One warp per row, persistent over rows.  A row is read once (through a shared-memory ring fed by bulk copies, two further
+// rows of the warp in flight), held in registers as packed fp32 pairs, reduced with warp shuffles (mean, then the centred
+// sum of squares, biased variance as src/triton_template/add_layernorm.py:33-55 and F.layer_norm do), and written once
+// with 128-bit stores; gamma and beta of a lane's columns stay in registers across rows.  Rows longer than 2048 elements are re-read from cache for the second and third sweep
 // instead of being held in registers.
 #include "stof_host.h"
 #include "stof_ptx.cuh"
@@ -87,41 +87,59 @@ layernorm_kernel(const __half* x, long long ldx, const __half* __restrict__ bias
             for (int s = 0; s < LN_STAGES - 1; ++s)
                 if (row + s * warps_total < rows) issue(row + s * warps_total, s);
         }
-        auto unpack = [](const uint4& u, float (&f)[8]) {
+        // 8 halves -> 4 packed fp32 pairs
+        auto unpack2 = [](const uint4& u, float2 (&f)[4]) {
             const __half2* h = reinterpret_cast<const __half2*>(&u);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float2 t = __half22float2(h[i]);
-                f[2 * i] = t.x;
-                f[2 * i + 1] = t.y;
-            }
+            for (int i = 0; i < 4; ++i) f[i] = __half22float2(h[i]);
         };
+        // gamma and beta of this lane's columns stay in registers as fp32 pairs for every row the warp processes
+        // (rows up to 1024 columns; longer rows convert them per row to bound the register count)
+        constexpr bool AFFINE_IN_REGS = NCHUNK <= 4;
+        float2 g2[AFFINE_IN_REGS ? NCHUNK : 1][4], b2[AFFINE_IN_REGS ? NCHUNK : 1][4];
+        if constexpr (AFFINE_IN_REGS) {
+#pragma unroll
+            for (int i = 0; i < NCHUNK; ++i) {
+                const int c = lane + 32 * i;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    g2[i][j] = make_float2(1.0f, 1.0f);
+                    b2[i][j] = make_float2(0.0f, 0.0f);
+                }
+                if (c < nchunks) {
+                    if (gamma) unpack2(__ldg(reinterpret_cast<const uint4*>(gamma + 8 * c)), g2[i]);
+                    if (beta) unpack2(__ldg(reinterpret_cast<const uint4*>(beta + 8 * c)), b2[i]);
+                }
+            }
+        }
         for (int it = 0; row < rows; row += warps_total, ++it) {
             const int s = it % LN_STAGES;
             const uint32_t parity = static_cast<uint32_t>((it / LN_STAGES) & 1);
             // completes with the copy (no partner thread involved); bounded all the same: ~1.6 s of suspended polls
             for (int spin = 0; !mbar_try_wait(&bars[s], parity) && spin < (1 << 14); ++spin) { }
             const unsigned char* src = ring + static_cast<size_t>(s) * slot_bytes;
-            float v[NCHUNK][8];
-            float sum = 0.f;
+            float2 v[NCHUNK][4];
+            float2 sum2 = make_float2(0.f, 0.f);
 #pragma unroll
             for (int i = 0; i < NCHUNK; ++i) {
                 const int c = lane + 32 * i;
-                if (c < nchunks) {
-                    unpack(*reinterpret_cast<const uint4*>(src + 16 * c), v[i]);
-                    float t[8];
-                    if (residual) {
-                        unpack(*reinterpret_cast<const uint4*>(src + row_bytes + 16 * c), t);
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) v[i][j] += t[j];
+                for (int j = 0; j < 4; ++j) v[i][j] = make_float2(0.f, 0.f);
+                if (c < nchunks) {
+                    unpack2(*reinterpret_cast<const uint4*>(src + 16 * c), v[i]);
+                    float2 t[4];
+                    if (residual) {
+                        unpack2(*reinterpret_cast<const uint4*>(src + row_bytes + 16 * c), t);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) v[i][j] = add2(v[i][j], t[j]);
                     }
                     if (bias) {
-                        unpack(__ldg(reinterpret_cast<const uint4*>(bias + 8 * c)), t);
+                        unpack2(__ldg(reinterpret_cast<const uint4*>(bias + 8 * c)), t);
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) v[i][j] += t[j];
+                        for (int j = 0; j < 4; ++j) v[i][j] = add2(v[i][j], t[j]);
                     }
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) sum += v[i][j];
+                    for (int j = 0; j < 4; ++j) sum2 = add2(sum2, v[i][j]);
                 }
             }
             // this slot is read out: refill the slot that was consumed one row ago with the row LN_STAGES - 1 ahead
@@ -131,35 +149,46 @@ layernorm_kernel(const __half* x, long long ldx, const __half* __restrict__ bias
                 const int ahead = row + (LN_STAGES - 1) * warps_total;
                 if (ahead < rows) issue(ahead, (it + LN_STAGES - 1) % LN_STAGES);
             }
-            const float mean = warp_sum(sum) * inv_n;
-            float sq = 0.f;
+            const float mean = warp_sum(sum2.x + sum2.y) * inv_n;
+            const float2 nmean2 = make_float2(-mean, -mean);
+            float2 sq2 = make_float2(0.f, 0.f);
 #pragma unroll
             for (int i = 0; i < NCHUNK; ++i) {
                 if (lane + 32 * i < nchunks) {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const float d = v[i][j] - mean;
-                        sq += d * d;
+                    for (int j = 0; j < 4; ++j) {
+                        v[i][j] = add2(v[i][j], nmean2);                  // centred value, kept for the output pass
+                        sq2 = fma2(v[i][j], v[i][j], sq2);
                     }
                 }
             }
-            const float rstd = 1.0f / sqrtf(warp_sum(sq) * inv_n + eps);
+            const float rstd = 1.0f / sqrtf(warp_sum(sq2.x + sq2.y) * inv_n + eps);
+            const float2 rstd2 = make_float2(rstd, rstd);
             __half* yr = y + static_cast<size_t>(row) * ldy;
 #pragma unroll
             for (int i = 0; i < NCHUNK; ++i) {
                 const int c = lane + 32 * i;
                 if (c < nchunks) {
-                    float g[8], b[8];
-                    if (gamma) unpack(__ldg(reinterpret_cast<const uint4*>(gamma + 8 * c)), g);
-                    if (beta) unpack(__ldg(reinterpret_cast<const uint4*>(beta + 8 * c)), b);
+                    float2 gg[4], bb[4];
+                    if constexpr (!AFFINE_IN_REGS) {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        float o = (v[i][j] - mean) * rstd;
-                        if (gamma) o *= g[j];
-                        if (beta) o += b[j];
-                        v[i][j] = o;
+                        for (int j = 0; j < 4; ++j) {
+                            gg[j] = make_float2(1.0f, 1.0f);
+                            bb[j] = make_float2(0.0f, 0.0f);
+                        }
+                        if (gamma) unpack2(__ldg(reinterpret_cast<const uint4*>(gamma + 8 * c)), gg);
+                        if (beta) unpack2(__ldg(reinterpret_cast<const uint4*>(beta + 8 * c)), bb);
                     }
-                    store8(yr + 8 * c, v[i]);
+                    uint4 u;
+                    __half2* h = reinterpret_cast<__half2*>(&u);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float2 g = AFFINE_IN_REGS ? g2[AFFINE_IN_REGS ? i : 0][j] : gg[j];
+                        const float2 bt = AFFINE_IN_REGS ? b2[AFFINE_IN_REGS ? i : 0][j] : bb[j];
+                        const float2 o = fma2(mul2(v[i][j], rstd2), g, bt);
+                        h[j] = __floats2half2_rn(o.x, o.y);
+                    }
+                    *reinterpret_cast<uint4*>(yr + 8 * c) = u;
                 }
             }
         }
@@ -232,20 +261,23 @@ extern "C" int stof_bias_residual_layernorm(const void* x, long long ldx, const 
     STOF_REQUIRE(aligned16(x) && aligned16(y) && aligned16(bias) && aligned16(residual) && aligned16(gamma) && aligned16(beta),
                  "layernorm: pointers must be 16-byte aligned");
     if (rows == 0) return STOF_OK;
-    // persistent grid: enough warps to keep the memory system busy, never more blocks than rows need
-    int blocks = (rows + LN_WARPS - 1) / LN_WARPS;
-    const int cap = sm_count() * LN_BLOCKS_PER_SM;
-    if (blocks > cap) blocks = cap;
-    const dim3 grid(blocks), block(LN_WARPS * 32);
+    const dim3 block(LN_WARPS * 32);
     const __half *xp = static_cast<const __half*>(x), *bp = static_cast<const __half*>(bias), *rp = static_cast<const __half*>(residual),
                  *gp = static_cast<const __half*>(gamma), *tp = static_cast<const __half*>(beta);
     __half* yp = static_cast<__half*>(y);
     const size_t ring_smem = hidden <= 2048 ? static_cast<size_t>(LN_WARPS) * LN_STAGES * (8 + static_cast<size_t>(hidden) * 2 * (residual ? 2 : 1)) : 0;
+    // persistent grid: as many blocks as are resident at once (registers and the ring decide), never more than the rows need
 #define STOF_LN_LAUNCH(N)                                                                                                           \
     do {                                                                                                                            \
         if (ring_smem > 48 * 1024)                                                                                                  \
             STOF_CUDA(cudaFuncSetAttribute(layernorm_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(ring_smem))); \
-        layernorm_kernel<N><<<grid, block, ring_smem, stream>>>(xp, ldx, bp, rp, ldr, gp, tp, eps, yp, ldy, rows, hidden);      \
+        int per_sm = 0;                                                                                                             \
+        STOF_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, layernorm_kernel<N>, LN_WARPS * 32, ring_smem));           \
+        if (per_sm < 1) per_sm = 1;                                                                                                 \
+        if (per_sm > LN_BLOCKS_PER_SM) per_sm = LN_BLOCKS_PER_SM;                                                                   \
+        int blocks = (rows + LN_WARPS - 1) / LN_WARPS;                                                                              \
+        if (blocks > sm_count() * per_sm) blocks = sm_count() * per_sm;                                                             \
+        layernorm_kernel<N><<<dim3(blocks), block, ring_smem, stream>>>(xp, ldx, bp, rp, ldr, gp, tp, eps, yp, ldy, rows, hidden);  \
     } while (0)
     if (hidden <= 256) STOF_LN_LAUNCH(1);
     else if (hidden <= 512) STOF_LN_LAUNCH(2);
