@@ -177,3 +177,34 @@ def test_t5_decoder_layer():
     torch.cuda.synchronize()
     want = of.t5_decoder_layer(hidden, params, torch.from_numpy(mask.astype(np.float32)), heads, 1e-5)
     assert _err(got, want) <= 3e-3 * max(1.0, want.abs().max().item())
+
+
+def test_encoder_config5_shapes_batch_independence():
+    """BERT-large shapes of configuration 5 (hidden 1024, 16 heads, FFN 4096, S = 4096, BigBird block mask, eps 1e-12) at
+    full sequence length: three layers on four sequences; every sequence is an independent shard, so running two of them
+    alone gives bit-identical rows (the property the multi-GPU batch sharding rests on), the result is finite and a second
+    run reproduces it; the first layer of one sequence is compared with the fp32 oracle on a sample of rows."""
+    import stof_b200
+    B, S, hid, heads, ffn = 4, 4096, 1024, 16, 4096
+    params = of.make_bert_params(hid, ffn, 3, seed=4)
+    g = torch.Generator().manual_seed(4)
+    hidden = torch.randn(B, S, hid, generator=g).half()
+    mask = om.recipe_mask("cfg5_bigbird_S4096_seed4")
+    layers = [stof_b200.EncoderWeights.from_dict(p, "cuda") for p in params]
+    enc = stof_b200.BertEncoder(layers, head_num=heads, eps=1e-12)
+    enc.set_mask(torch.from_numpy(mask).cuda())
+    full = enc(hidden.cuda()).clone()
+    torch.cuda.synchronize()
+    assert torch.isfinite(full.float()).all()
+    assert torch.equal(enc(hidden.cuda()), full)
+    part = stof_b200.BertEncoder(layers, head_num=heads, eps=1e-12)
+    part.set_mask(torch.from_numpy(mask).cuda())
+    assert torch.equal(part(hidden[1:3].cuda()), full[1:3])
+    # one layer, one sequence against the oracle (dense fp32 attention of a 4096 x 4096 score matrix per head on the CPU)
+    one = stof_b200.BertEncoder(layers[:1], head_num=heads, eps=1e-12)
+    one.set_mask(torch.from_numpy(mask).cuda())
+    got = one(hidden[:1].cuda())
+    torch.cuda.synchronize()
+    want = of.bert_layer(hidden[:1], params[0], torch.from_numpy(mask.astype(np.float32)), heads, eps=1e-12)
+    rows = torch.arange(0, S, 37)
+    assert _err(got[:, rows], want[:, rows]) <= 2e-3 * max(1.0, want.abs().max().item())
