@@ -6,18 +6,22 @@
 // PLAN built once per block index (plan_kernel): per query tile the ordered tile list and, per tile, one
 // code for each 16-row x 16-column group (0 absent, 1 full, 2+i partial tile i of the row block).
 //
-// Kernel.  Persistent, two thread blocks per SM, static schedule over the items (heavy query tiles first
-// inside groups of (batch, head) pairs small enough to keep their K/V in L2):
-//   warp 4      TMA producer: Q tiles (double buffered) and (K, V) tile pairs through a ring of stages
-//   warp 5      MMA issuer:   S = Q K^T (128 x 64 x 64) into one of two S buffers in tensor memory, and
-//               O += P V with P read back from tensor memory (fp16, stored over the S buffer it came from)
-//               and V consumed in its natural key-row-major layout through an MN-major descriptor;
-//               O is double buffered across items so that an item's epilogue overlaps the next item
-//   warps 0-3   softmax: one query row per thread (tensor-memory lane): tcgen05.ld of the scores, masking
-//               from the plan codes, exp2 with the scale folded into one FMA, running maximum with a lazy
-//               rescale of O (only when the maximum grew by more than 2^8), P written with tcgen05.st,
-//               final O / l normalisation and 128-bit stores
-// Row groups that do not list a tile skip its exponentials (P = 0); tiles nobody lists are never loaded.
+// Kernel.  Persistent, two thread blocks per SM, static schedule over the items (heavy query tiles first inside groups of
+// (batch, head) pairs small enough to keep their K/V in L2).
+//   warp 4      TMA producer: Q tile of the next item (double-buffered), K tiles through a ring of four slots, V tiles through
+//               a ring of three
+//   warp 5      MMA issuer:   S = Q K^T (128 x 64 x 64) into one of THREE S buffers in tensor memory, up to three tiles ahead
+//               of the PV products; O += P V with P read back from tensor memory (fp16) and V consumed in its natural
+//               key-row-major layout through an MN-major descriptor
+//   warps 0-3   softmax: one query row per thread (tensor-memory lane): tcgen05.ld of the scores, masking from the plan
+//               codes, row maximum (3-input max), exp2 with scale and maximum folded into packed FMAs (part of the
+//               exponentials on the FMA pipe by polynomial), lazy rescale of O (only when the maximum grew by more than
+//               2^8), P written with tcgen05.st, final O / l normalisation staged in shared memory and written with TMA stores
+// The M = 128 tile covers two 64-row mask blocks; a key tile that only one of them lists keeps only half of the softmax warps
+// busy (the others store P = 0 at once and move on).  With three S buffers the two halves may drift up to three tiles apart,
+// so a run of tiles listed alternately by the upper and the lower block is worked on by both halves at the same time.
+// Masking of partial tiles and the rescale of O are out-of-line functions that work on tensor memory in place.
+// Tiles nobody lists are never loaded.
 #include "stof_host.h"
 #include "stof_ptx.cuh"
 
@@ -25,15 +29,15 @@ namespace stof {
 namespace {
 
 constexpr int A_TQ = 128, A_TKV = 64, A_D = 64;
-constexpr int A_STAGES = 3;
+constexpr int A_SBUF = 3;                         // S buffers in tensor memory: QK^T runs up to three tiles ahead of PV
+constexpr int A_KSLOTS = 4, A_VSLOTS = 3;         // K ring (tiles g+1..g+3 and one in flight) and V ring
 constexpr int A_Q_BYTES = A_TQ * A_D * 2;         // 16 KB per Q buffer
-constexpr int A_KV_BYTES = A_TKV * A_D * 2;       // 8 KB each for K and V
-constexpr int A_STAGE_BYTES = 2 * A_KV_BYTES;
+constexpr int A_KV_BYTES = A_TKV * A_D * 2;       // 8 KB per K or V tile
 constexpr int A_OSTAGE_BYTES = 32 * A_D * 2;     // 4 KB output staging per softmax warp (TMA store source)
 constexpr int A_THREADS = 192;
 constexpr int A_CTAS_PER_SM = 2;
 constexpr int A_TMEM_COLS = 256;
-constexpr int A_COL_S = 0, A_COL_O = 128;         // S0 @0, S1 @64 (P overlays the first 32 columns of its S), O0 @128, O1 @192
+constexpr int A_COL_S = 0, A_COL_O = 192;         // S0 @0, S1 @64, S2 @128 (P overlays the first 32 columns of its S), O @192
 constexpr int A_MAX_TABLE_BYTES = 48 * 1024;
 constexpr float A_RESCALE_THRESHOLD = 8.0f;       // log2 units
 #ifndef A_POLY_PAIRS
@@ -42,8 +46,9 @@ constexpr float A_RESCALE_THRESHOLD = 8.0f;       // log2 units
 constexpr int A_GROUP_BH = 40;                    // (batch, head) pairs per scheduling group: 40 x 2 x S x 128 B of K/V stay in L2
 
 enum {
-    AB_Q_FULL = 0, AB_Q_EMPTY = 2, AB_KV_FULL = 4, AB_KV_EMPTY = AB_KV_FULL + A_STAGES, AB_S_FULL = AB_KV_EMPTY + A_STAGES,
-    AB_P_FULL = AB_S_FULL + 2, AB_PV_DONE = AB_P_FULL + 2, AB_O_FREE = AB_PV_DONE + 2, AB_COUNT = AB_O_FREE + 2
+    AB_Q_FULL = 0, AB_Q_EMPTY = 2, AB_O_FREE = 4, AB_S_FULL = 5, AB_P_FULL = AB_S_FULL + A_SBUF, AB_PV_DONE = AB_P_FULL + A_SBUF,
+    AB_K_FULL = AB_PV_DONE + A_SBUF, AB_K_EMPTY = AB_K_FULL + A_KSLOTS, AB_V_FULL = AB_K_EMPTY + A_KSLOTS,
+    AB_V_EMPTY = AB_V_FULL + A_VSLOTS, AB_COUNT = AB_V_EMPTY + A_VSLOTS
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -282,8 +287,9 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     unsigned char* q_smem = smem;                                   // 2 buffers
-    unsigned char* kv_smem = q_smem + 2 * A_Q_BYTES;
-    unsigned char* o_smem = kv_smem + A_STAGES * A_STAGE_BYTES;      // 4 x 4 KB, one slab per softmax warp
+    unsigned char* k_smem = q_smem + 2 * A_Q_BYTES;
+    unsigned char* v_smem = k_smem + A_KSLOTS * A_KV_BYTES;
+    unsigned char* o_smem = v_smem + A_VSLOTS * A_KV_BYTES;          // 4 x 4 KB, one slab per softmax warp
     uint64_t* bars = reinterpret_cast<uint64_t*>(o_smem + 4 * A_OSTAGE_BYTES);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + AB_COUNT);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -299,14 +305,20 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         for (int i = 0; i < 2; ++i) {
             mbar_init(&bars[AB_Q_FULL + i], 1);
             mbar_init(&bars[AB_Q_EMPTY + i], 1);
+        }
+        mbar_init(&bars[AB_O_FREE], 4);
+        for (int i = 0; i < A_SBUF; ++i) {
             mbar_init(&bars[AB_S_FULL + i], 1);
             mbar_init(&bars[AB_P_FULL + i], 4);
             mbar_init(&bars[AB_PV_DONE + i], 1);
-            mbar_init(&bars[AB_O_FREE + i], 4);
         }
-        for (int i = 0; i < A_STAGES; ++i) {
-            mbar_init(&bars[AB_KV_FULL + i], 1);
-            mbar_init(&bars[AB_KV_EMPTY + i], 1);
+        for (int i = 0; i < A_KSLOTS; ++i) {
+            mbar_init(&bars[AB_K_FULL + i], 1);
+            mbar_init(&bars[AB_K_EMPTY + i], 1);
+        }
+        for (int i = 0; i < A_VSLOTS; ++i) {
+            mbar_init(&bars[AB_V_FULL + i], 1);
+            mbar_init(&bars[AB_V_EMPTY + i], 1);
         }
         fence_mbar_init();
     }
@@ -326,33 +338,52 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 tma_prefetch_desc(&map_q);
                 tma_prefetch_desc(&map_k);
                 tma_prefetch_desc(&map_v);
-                int it = 0;
-                long long g = 0;
-                Item item = fetch_item(0, p, plan_sched);
-                for (unsigned k = 0; item.valid; ++k) {
-                    const Item next = fetch_item(k + 1, p, plan_sched);      // its loads complete while this item streams
-                    const Item cur = item;
-                    item = next;
-                    const int n = cur.n;
-                    if (n == 0) continue;
-                    const int qb = it & 1;
-                    mbar_wait(&bars[AB_Q_EMPTY + qb], ((it >> 1) & 1) ^ 1, wctx, AB_Q_EMPTY + qb);
-                    mbar_arrive_expect_tx(&bars[AB_Q_FULL + qb], A_Q_BYTES);
-                    tma_tile(q_smem + qb * A_Q_BYTES, &map_q, &bars[AB_Q_FULL + qb], cur.qt * A_TQ, cur.head, cur.batch, p.slot_s[0],
-                             p.slot_h[0], p.slot_b[0]);
-                    const uint16_t* tl = plan_tiles + static_cast<size_t>(cur.qt) * p.max_tiles;
-                    for (int j = 0; j < n; ++j, ++g) {
-                        const int s = static_cast<int>(g % A_STAGES);
-                        const uint32_t ph = static_cast<uint32_t>((g / A_STAGES) & 1);
-                        mbar_wait(&bars[AB_KV_EMPTY + s], ph ^ 1, wctx, AB_KV_EMPTY + s);
-                        const int kv_row = static_cast<int>(tl[j]) * A_TKV;
-                        unsigned char* k_dst = kv_smem + s * A_STAGE_BYTES;
-                        mbar_arrive_expect_tx(&bars[AB_KV_FULL + s], A_STAGE_BYTES);
-                        tma_tile(k_dst, &map_k, &bars[AB_KV_FULL + s], kv_row, cur.head, cur.batch, p.slot_s[1], p.slot_h[1], p.slot_b[1]);
-                        tma_tile(k_dst + A_KV_BYTES, &map_v, &bars[AB_KV_FULL + s], kv_row, cur.head, cur.batch, p.slot_s[2], p.slot_h[2],
-                                 p.slot_b[2]);
+                // two cursors over the block's stream of steps (tiles of its items with tiles): K loads run A_SBUF steps ahead of
+                // the V loads, in the order the MMA warp consumes them.  `it` counts the items with tiles (Q buffers alternate).
+                struct Cursor { unsigned k; Item item; int j, it; };
+                auto settle = [&](Cursor& c) {
+                    for (;;) {
+                        c.item = fetch_item(c.k, p, plan_sched);
+                        if (!c.item.valid || c.item.n > 0) return;
+                        ++c.k;
                     }
-                    ++it;
+                };
+                auto advance = [&](Cursor& c) {
+                    if (++c.j >= c.item.n) { c.j = 0; ++c.k; ++c.it; settle(c); }
+                };
+                Cursor kc, vc;
+                kc.k = 0; kc.j = 0; kc.it = 0;
+                settle(kc);
+                vc = kc;
+                unsigned uk = 0, uv = 0;
+                auto load_k = [&]() {
+                    if (kc.j == 0) {
+                        const int qb = kc.it & 1;
+                        mbar_wait(&bars[AB_Q_EMPTY + qb], static_cast<uint32_t>(((kc.it >> 1) & 1) ^ 1), wctx, AB_Q_EMPTY + qb);
+                        mbar_arrive_expect_tx(&bars[AB_Q_FULL + qb], A_Q_BYTES);
+                        tma_tile(q_smem + qb * A_Q_BYTES, &map_q, &bars[AB_Q_FULL + qb], kc.item.qt * A_TQ, kc.item.head, kc.item.batch, p.slot_s[0],
+                                 p.slot_h[0], p.slot_b[0]);
+                    }
+                    const int sl = static_cast<int>(uk % A_KSLOTS);
+                    mbar_wait(&bars[AB_K_EMPTY + sl], ((uk / A_KSLOTS) & 1) ^ 1, wctx, AB_K_EMPTY + sl);
+                    const int tile = plan_tiles[static_cast<size_t>(kc.item.qt) * p.max_tiles + kc.j];
+                    mbar_arrive_expect_tx(&bars[AB_K_FULL + sl], A_KV_BYTES);
+                    tma_tile(k_smem + sl * A_KV_BYTES, &map_k, &bars[AB_K_FULL + sl], tile * A_TKV, kc.item.head, kc.item.batch, p.slot_s[1], p.slot_h[1],
+                             p.slot_b[1]);
+                    advance(kc);
+                    ++uk;
+                };
+                for (int i = 0; i < A_SBUF && kc.item.valid; ++i) load_k();
+                while (vc.item.valid) {
+                    const int sl = static_cast<int>(uv % A_VSLOTS);
+                    mbar_wait(&bars[AB_V_EMPTY + sl], ((uv / A_VSLOTS) & 1) ^ 1, wctx, AB_V_EMPTY + sl);
+                    const int tile = plan_tiles[static_cast<size_t>(vc.item.qt) * p.max_tiles + vc.j];
+                    mbar_arrive_expect_tx(&bars[AB_V_FULL + sl], A_KV_BYTES);
+                    tma_tile(v_smem + sl * A_KV_BYTES, &map_v, &bars[AB_V_FULL + sl], tile * A_TKV, vc.item.head, vc.item.batch, p.slot_s[2], p.slot_h[2],
+                             p.slot_b[2]);
+                    advance(vc);
+                    ++uv;
+                    if (kc.item.valid) load_k();
                 }
             }
         } else if (warp == 5) {
@@ -360,70 +391,65 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             if (elect_one()) {
                 constexpr uint32_t idesc_qk = make_idesc_f16(A_TQ, A_TKV, /*b_mn_major=*/false);
                 constexpr uint32_t idesc_pv = make_idesc_f16(A_TQ, A_D, /*b_mn_major=*/true);
-                // S = Q K^T of global step g, reading Q buffer qb
-                auto issue_qk = [&](long long g, int qb) {
-                    const int s = static_cast<int>(g % A_STAGES);
-                    mbar_wait(&bars[AB_KV_FULL + s], static_cast<uint32_t>((g / A_STAGES) & 1), wctx, AB_KV_FULL + s);
+                // two cursors over the same stream of steps: the QK^T cursor runs A_SBUF steps ahead of the PV cursor
+                struct Cursor { unsigned k; int n, j, it; bool valid; };
+                auto settle = [&](Cursor& c) {
+                    for (;;) {
+                        const Item item = fetch_item(c.k, p, plan_sched);
+                        c.valid = item.valid;
+                        c.n = item.n;
+                        if (!item.valid || item.n > 0) return;
+                        ++c.k;
+                    }
+                };
+                auto advance = [&](Cursor& c) {
+                    if (++c.j >= c.n) { c.j = 0; ++c.k; ++c.it; settle(c); }
+                };
+                Cursor qk, pv;
+                qk.k = 0; qk.j = 0; qk.it = 0;
+                settle(qk);
+                pv = qk;
+                unsigned uq = 0, u = 0;
+                // S = Q K^T of step uq into buffer uq % A_SBUF.  The buffer held S and P of step uq - A_SBUF: the PV product that read
+                // that P was issued before and the tensor core executes this thread's MMAs in order.
+                auto issue_qk = [&]() {
+                    const int qb = qk.it & 1;
+                    if (qk.j == 0) mbar_wait(&bars[AB_Q_FULL + qb], static_cast<uint32_t>((qk.it >> 1) & 1), wctx, AB_Q_FULL + qb);
+                    const int sl = static_cast<int>(uq % A_KSLOTS);
+                    mbar_wait(&bars[AB_K_FULL + sl], (uq / A_KSLOTS) & 1, wctx, AB_K_FULL + sl);
                     tc_fence_after();
                     const uint32_t q_addr = smem_u32(q_smem + qb * A_Q_BYTES);
-                    const uint32_t k_addr = smem_u32(kv_smem + s * A_STAGE_BYTES);
-                    const uint32_t d = tmem_base + A_COL_S + static_cast<uint32_t>(g & 1) * A_TKV;
+                    const uint32_t k_addr = smem_u32(k_smem + sl * A_KV_BYTES);
+                    const int sb = static_cast<int>(uq % A_SBUF);
+                    const uint32_t d = tmem_base + A_COL_S + sb * A_TKV;
 #pragma unroll
                     for (int kk = 0; kk < A_D / 16; ++kk)
                         mma_f16_ss(d, make_smem_desc_sw128(q_addr + kk * 32, 16, 1024), make_smem_desc_sw128(k_addr + kk * 32, 16, 1024),
                                    idesc_qk, kk > 0 ? 1u : 0u);
-                    tc_commit(&bars[AB_S_FULL + (g & 1)]);
+                    tc_commit(&bars[AB_K_EMPTY + sl]);
+                    tc_commit(&bars[AB_S_FULL + sb]);
+                    if (qk.j == qk.n - 1) tc_commit(&bars[AB_Q_EMPTY + qb]);     // every QK^T of that item has been issued
+                    advance(qk);
+                    ++uq;
                 };
-                // next non-empty item of this thread block, starting at schedule position k
-                auto next_item = [&](unsigned& k, int& n) -> bool {
-                    for (;;) {
-                        const Item item = fetch_item(k, p, plan_sched);
-                        if (!item.valid) return false;
-                        ++k;
-                        n = item.n;
-                        if (n > 0) return true;
-                    }
-                };
-                unsigned k = 0;
-                long long g = 0;
-                int it = 0, n = 0, n_next = 0;
-                bool have = next_item(k, n);
-                if (have) {
-                    mbar_wait(&bars[AB_Q_FULL + 0], 0, wctx, AB_Q_FULL);
-                    issue_qk(0, 0);
-                }
-                while (have) {
-                    const bool have_next = next_item(k, n_next);
-                    const int qb = it & 1;
-                    for (int j = 0; j < n; ++j, ++g) {
-                        if (j + 1 < n) {
-                            issue_qk(g + 1, qb);
-                        } else {
-                            tc_commit(&bars[AB_Q_EMPTY + qb]);                   // every QK^T of this item has been issued
-                            if (have_next) {
-                                const int qn = (it + 1) & 1;
-                                mbar_wait(&bars[AB_Q_FULL + qn], static_cast<uint32_t>(((it + 1) >> 1) & 1), wctx, AB_Q_FULL + qn);
-                                issue_qk(g + 1, qn);
-                            }
-                        }
-                        if (j == 0) {
-                            mbar_wait(&bars[AB_O_FREE + qb], static_cast<uint32_t>(((it >> 1) & 1) ^ 1), wctx, AB_O_FREE + qb);
-                        }
-                        const int b = static_cast<int>(g & 1), s = static_cast<int>(g % A_STAGES);
-                        mbar_wait(&bars[AB_P_FULL + b], static_cast<uint32_t>((g >> 1) & 1), wctx, AB_P_FULL + b);
-                        tc_fence_after();
-                        const uint32_t v_addr = smem_u32(kv_smem + s * A_STAGE_BYTES + A_KV_BYTES);
-                        const uint32_t d = tmem_base + A_COL_O + qb * A_D;
-                        const uint32_t p_tmem = tmem_base + A_COL_S + b * A_TKV;
+                for (int i = 0; i < A_SBUF && qk.valid; ++i) issue_qk();
+                while (pv.valid) {
+                    if (pv.j == 0) mbar_wait(&bars[AB_O_FREE], static_cast<uint32_t>((pv.it & 1) ^ 1), wctx, AB_O_FREE);     // the previous item's O was read
+                    const int sb = static_cast<int>(u % A_SBUF), sl = static_cast<int>(u % A_VSLOTS);
+                    mbar_wait(&bars[AB_P_FULL + sb], (u / A_SBUF) & 1, wctx, AB_P_FULL + sb);
+                    mbar_wait(&bars[AB_V_FULL + sl], (u / A_VSLOTS) & 1, wctx, AB_V_FULL + sl);
+                    tc_fence_after();
+                    const uint32_t v_addr = smem_u32(v_smem + sl * A_KV_BYTES);
+                    const uint32_t p_tmem = tmem_base + A_COL_S + sb * A_TKV;
 #pragma unroll
-                        for (int kk = 0; kk < A_TKV / 16; ++kk)
-                            mma_f16_ts(d, p_tmem + kk * 8, make_smem_desc_sw128(v_addr + kk * 2048, 16, 1024), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
-                        tc_commit(&bars[AB_KV_EMPTY + s]);
-                        tc_commit(&bars[AB_PV_DONE + b]);
-                    }
-                    ++it;
-                    n = n_next;
-                    have = have_next;
+                    for (int kk = 0; kk < A_TKV / 16; ++kk)
+                        mma_f16_ts(tmem_base + A_COL_O, p_tmem + kk * 8, make_smem_desc_sw128(v_addr + kk * 2048, 16, 1024), idesc_pv,
+                                   (pv.j > 0 || kk > 0) ? 1u : 0u);
+                    tc_commit(&bars[AB_V_EMPTY + sl]);
+                    tc_commit(&bars[AB_PV_DONE + sb]);
+                    advance(pv);
+                    ++u;
+                    if (qk.valid) issue_qk();                                     // into the buffer this PV has just been issued for
                 }
             }
         } else {
@@ -432,8 +458,7 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
             const int rg = lr >> 4;                          // 16-row group inside the query tile
             const float scale = p.scale_log2, inv_scale = 1.0f / p.scale_log2;
-            long long g = 0;
-            int it = 0;
+            unsigned g = 0;                                  // steps of this block so far (matches the MMA warp's count)
             // per-item values that need global loads are fetched one item ahead (no dependent-load chain at item boundaries)
             auto item_row_base = [&](const Item& x) -> int {
                 const int r = x.qt * A_TQ + lr;
@@ -481,21 +506,20 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     store_rows(z, cur_item);
                     continue;
                 }
-                const int ob = it & 1;
                 const uint2* my_codes = item_codes(cur_item);
                 const uint16_t* tl = plan_tiles + static_cast<size_t>(cur_item.qt) * p.max_tiles;
                 const int row_in_block = row & (p.bm - 1);
                 float m_ref = -INFINITY, l_sum = 0.f;
 
                 for (int j = 0; j < n; ++j, ++g) {
-                    const int b = static_cast<int>(g & 1);
+                    const int b = static_cast<int>(g % A_SBUF);
                     const uint2 cur = cw;
                     if (j + 1 < n) cw = __ldg(my_codes + (j + 1) * 8);     // 32 codes = 64 B = 8 uint2 per tile
                     const bool all_absent = (cur.x | cur.y) == 0u;
                     const bool all_full = cur.x == 0x00010001u && cur.y == 0x00010001u;
                     const bool warp_absent = __all_sync(0xffffffffu, all_absent);
                     const bool warp_full = __all_sync(0xffffffffu, all_full);
-                    mbar_wait(&bars[AB_S_FULL + b], static_cast<uint32_t>((g >> 1) & 1), wctx, AB_S_FULL + b);
+                    mbar_wait(&bars[AB_S_FULL + b], (g / A_SBUF) & 1, wctx, AB_S_FULL + b);
                     tc_fence_after();
                     uint32_t r0[32], r1[32];
                     if (warp_absent) {
@@ -531,10 +555,10 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                             }
                             if (j > 0) {
                                 // every PV product issued so far for this item must have landed in O before it is rescaled
-                                const int pb = static_cast<int>((g - 1) & 1);
-                                mbar_wait(&bars[AB_PV_DONE + pb], static_cast<uint32_t>(((g - 1) >> 1) & 1), wctx, AB_PV_DONE + pb);
+                                const int pb = static_cast<int>((g - 1) % A_SBUF);
+                                mbar_wait(&bars[AB_PV_DONE + pb], ((g - 1) / A_SBUF) & 1, wctx, AB_PV_DONE + pb);
                                 tc_fence_after();
-                                rescale_o_in_tmem(t_lane + A_COL_O + ob * A_D, alpha);
+                                rescale_o_in_tmem(t_lane + A_COL_O, alpha);
                             }
                         }
                         // P = 2^(s * scale - m) for the 64 scores in r0/r1: pairs of columns with packed fp32 FMAs; A_POLY_PAIRS of
@@ -576,16 +600,16 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 }
                 // ---------------------------------------------------------- item epilogue: O / l -> fp16 -> global
                 {
-                    const int pb = static_cast<int>((g - 1) & 1);
-                    mbar_wait(&bars[AB_PV_DONE + pb], static_cast<uint32_t>(((g - 1) >> 1) & 1), wctx, AB_PV_DONE + pb);
+                    const int pb = static_cast<int>((g - 1) % A_SBUF);
+                    mbar_wait(&bars[AB_PV_DONE + pb], ((g - 1) / A_SBUF) & 1, wctx, AB_PV_DONE + pb);
                     tc_fence_after();
                     uint32_t o0[32], o1[32];
-                    tmem_ld32(t_lane + A_COL_O + ob * A_D, o0);
-                    tmem_ld32(t_lane + A_COL_O + ob * A_D + 32, o1);
+                    tmem_ld32(t_lane + A_COL_O, o0);
+                    tmem_ld32(t_lane + A_COL_O + 32, o1);
                     tc_wait_ld();
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&bars[AB_O_FREE + ob]);
+                    if (lane == 0) mbar_arrive(&bars[AB_O_FREE]);
                     {
                         const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.0f;
                         uint4 u[8];
@@ -600,7 +624,6 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                         store_rows(u, cur_item);
                     }
                 }
-                ++it;
             }
             if (lane == 0) tma_store_wait_all();             // every output store of this warp has been performed
         }
@@ -613,7 +636,7 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     }
 }
 
-constexpr size_t A_SMEM_BYTES = 1024 + 2 * A_Q_BYTES + static_cast<size_t>(A_STAGES) * A_STAGE_BYTES + 4 * A_OSTAGE_BYTES + AB_COUNT * 8 + 16;
+constexpr size_t A_SMEM_BYTES = 1024 + 2 * A_Q_BYTES + static_cast<size_t>(A_KSLOTS + A_VSLOTS) * A_KV_BYTES + 4 * A_OSTAGE_BYTES + AB_COUNT * 8 + 16;
 
 // Sorts the three outer dimensions (row, head, batch) by stride so that the tensor map's strides ascend;
 // returns the coordinate slot of each logical dimension.
