@@ -307,8 +307,8 @@ def run_attention(args, rank, world, local):
     mask_bytes = mask.numel() * 2
     comp_best = min(comp_ms)
     achieved = flops / (dev_ms / args.steps * 1e-3) / 1e12       # this rank's kernel
-    # DRAM read+write bytes of one launch from an ncu capture at batch 8 of the same mask (88.2 MB), scaled by batch
-    traffic = 88.196e6 * cfg.batch / 8 if cfg.mask == "bigbird" and cfg.seq_len == 2048 and cfg.heads == 12 else None
+    # DRAM read+write bytes of one launch from an ncu capture at batch 8 of the same mask (86.2 MB), scaled by batch
+    traffic = 86.230e6 * cfg.batch / 8 if cfg.mask == "bigbird" and cfg.seq_len == 2048 and cfg.heads == 12 else None
     line = {
         "metric": "masked-MHA effective TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
