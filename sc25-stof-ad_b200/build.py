@@ -55,7 +55,7 @@ def build_library(verbose: bool = False, force: bool = False) -> str:
         failed |= pr.returncode != 0
     if failed:
         raise RuntimeError("nvcc failed")
-    subprocess.check_call([nvcc, "-shared", "-o", LIB, *objs, "-cudart", "static", "-Xcompiler", "-fPIC"])
+    subprocess.check_call([nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB, *objs, "-cudart", "static", "-Xcompiler", "-fPIC"])
     return LIB
 
 
