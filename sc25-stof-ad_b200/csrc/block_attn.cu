@@ -436,8 +436,8 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 while (pv.valid) {
                     if (pv.j == 0) mbar_wait(&bars[AB_O_FREE], static_cast<uint32_t>((pv.it & 1) ^ 1), wctx, AB_O_FREE);     // the previous item's O was read
                     const int sb = static_cast<int>(u % A_SBUF), sl = static_cast<int>(u % A_VSLOTS);
+                    mbar_wait(&bars[AB_V_FULL + sl], (u / A_VSLOTS) & 1, wctx, AB_V_FULL + sl);      // long there: off the P -> PV path
                     mbar_wait(&bars[AB_P_FULL + sb], (u / A_SBUF) & 1, wctx, AB_P_FULL + sb);
-                    mbar_wait(&bars[AB_V_FULL + sl], (u / A_VSLOTS) & 1, wctx, AB_V_FULL + sl);
                     tc_fence_after();
                     const uint32_t v_addr = smem_u32(v_smem + sl * A_KV_BYTES);
                     const uint32_t p_tmem = tmem_base + A_COL_S + sb * A_TKV;
