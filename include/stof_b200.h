@@ -125,6 +125,26 @@ int stof_block_attn(const void* q, const void* k, const void* v, void* out,
                     int block_m, int block_n, int num_warps, float softmax_scale,
                     int* status_dev, void* stream);
 
+/* stof_block_attn with the deal of the work items to the thread blocks given by the caller.  No counterpart in the
+ * reference (its kernels take one 64-row block per thread block from the launch grid,
+ * src/ops/src/block_attn_mask_cuda.cu:6026-6316); here the kernel is persistent and a work item is one 128-row query tile
+ * of one (batch, head).  By default the items are dealt round-robin, heaviest tiles first; query tiles with very different
+ * tile counts then leave some blocks with up to 10-20 % more steps than the average.  `schedule` (device, int32) lets the
+ * host balance them, e.g. by a longest-processing-time assignment over the per-tile counts that the plan holds
+ * (stof_b200/attention.py: attention_schedule):
+ *   schedule[0] = G (thread blocks, 1 <= G <= 2 x SMs), schedule[1 .. G + 1] = offsets, then the item ids,
+ *   id = (batch_index * heads + head_index) * ceil(seq_len / 128) + query_tile; block b works through
+ *   ids[offset[b] .. offset[b + 1]) in that order.  Every item must appear exactly once (items left out are not computed).
+ * `schedule_blocks` repeats G for validation on the host. */
+int stof_block_attn_scheduled(const void* q, const void* k, const void* v, void* out,
+                              int batch, int heads, int seq_len, int head_dim,
+                              const long long q_strides[3], const long long k_strides[3],
+                              const long long v_strides[3], const long long out_strides[3],
+                              const int* part_row_ptr, const void* part_block_mask, const void* plan,
+                              int block_m, int block_n, int num_warps, float softmax_scale,
+                              const int* schedule, int schedule_blocks,
+                              int* status_dev, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * GEMM with fused epilogue: C[M,N] = epilogue(A[M,K] @ W[K,N] + bias[N]), fp16 in/out, fp32 accumulate.
  * Replaces: the Triton templates of src/triton_template/ (gemm_add_layernorm.py:77-144,

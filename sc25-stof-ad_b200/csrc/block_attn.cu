@@ -179,6 +179,7 @@ struct AttnParams {
     int slot_s[4], slot_h[4], slot_b[4];   // coordinate slot (1..3) of row / head / batch in the q, k, v, out tensor maps
     float scale_log2;
     int* status;
+    const int* schedule;                   // optional caller-made deal of the items to the thread blocks (see fetch_item)
 };
 
 __device__ __forceinline__ void tma_tile(void* dst, const CUtensorMap* map, uint64_t* bar, int row, int h, int b, int ss, int sh, int sb) {
@@ -195,8 +196,10 @@ __device__ __forceinline__ void tma_tile_store(const CUtensorMap* map, const voi
     tma_store_4d(map, src, 0, c1, c2, c3);
 }
 
-// Static schedule: items are enumerated group by group ((batch, head) pairs in chunks of A_GROUP_BH), inside a
-// group query-tile-rank major (heaviest tiles first), and dealt round-robin to the thread blocks.
+// Static schedule.  Default: items are enumerated group by group ((batch, head) pairs in chunks of A_GROUP_BH), inside a
+// group query-tile-rank major (heaviest tiles first), and dealt round-robin to the thread blocks.  With a schedule table
+// ({blocks G, G + 1 offsets, item ids = (batch * heads + head) * query tiles + query tile}, made by the caller, e.g. by a
+// longest-processing-time assignment over the tile counts) block b walks ids[offset[b] .. offset[b + 1]).
 struct Item {
     int qt, head, batch, n;
     bool valid;
@@ -204,6 +207,23 @@ struct Item {
 __device__ __forceinline__ Item fetch_item(unsigned k, const AttnParams& p, const int2* sched) {
     Item it;
     it.qt = 0; it.head = 0; it.batch = 0; it.n = 0;
+    if (p.schedule != nullptr) {
+        const int b0 = __ldg(p.schedule + 1 + blockIdx.x), b1 = __ldg(p.schedule + 2 + blockIdx.x);
+        it.valid = static_cast<long long>(k) < static_cast<long long>(b1) - b0;
+        if (!it.valid) return it;
+        const unsigned id = static_cast<unsigned>(__ldg(p.schedule + 2 + gridDim.x + b0 + static_cast<int>(k)));
+        if (id >= p.total_items) {                       // a table that does not belong to this launch: stop, and say so
+            if (p.status) atomicCAS(p.status, 0, STATUS_BAD_INDEX);
+            it.valid = false;
+            return it;
+        }
+        const unsigned bh = id / static_cast<unsigned>(p.n_qtiles);
+        it.qt = static_cast<int>(id - bh * static_cast<unsigned>(p.n_qtiles));
+        it.n = __ldg(reinterpret_cast<const int*>(p.plan + plan_off_ntiles()) + it.qt);
+        it.batch = static_cast<int>(bh / p.heads);
+        it.head = static_cast<int>(bh - it.batch * p.heads);
+        return it;
+    }
     const unsigned idx = blockIdx.x + k * gridDim.x;
     it.valid = idx < p.total_items;
     if (!it.valid) return it;
@@ -721,10 +741,11 @@ extern "C" int stof_block_attn_plan(const int* full_row_ptr, const int* full_col
     return STOF_OK;
 }
 
-extern "C" int stof_block_attn(const void* q, const void* k, const void* v, void* out, int batch, int heads, int seq_len, int head_dim,
-                               const long long q_strides[3], const long long k_strides[3], const long long v_strides[3],
-                               const long long out_strides[3], const int* part_row_ptr, const void* part_block_mask, const void* plan,
-                               int block_m, int block_n, int num_warps, float softmax_scale, int* status_dev, void* stream_) {
+static int launch_block_attn(const void* q, const void* k, const void* v, void* out, int batch, int heads, int seq_len, int head_dim,
+                             const long long q_strides[3], const long long k_strides[3], const long long v_strides[3],
+                             const long long out_strides[3], const int* part_row_ptr, const void* part_block_mask, const void* plan,
+                             int block_m, int block_n, int num_warps, float softmax_scale, const int* schedule, int schedule_blocks,
+                             int* status_dev, void* stream_) {
     (void)num_warps;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     STOF_REQUIRE(q && k && v && out, "block_attn: null q/k/v/out");
@@ -751,6 +772,7 @@ extern "C" int stof_block_attn(const void* q, const void* k, const void* v, void
     p.max_tiles = (seq_len + A_TKV - 1) / A_TKV;
     p.scale_log2 = softmax_scale * 1.4426950408889634f;
     p.status = status_dev;
+    p.schedule = schedule;
     const long long items = static_cast<long long>(batch) * heads * p.n_qtiles;
     STOF_REQUIRE(items < (1ll << 31), "block_attn: batch * heads * query tiles beyond 2^31");
     p.total_items = static_cast<unsigned>(items);
@@ -770,7 +792,32 @@ extern "C" int stof_block_attn(const void* q, const void* k, const void* v, void
     }
     long long grid = static_cast<long long>(A_CTAS_PER_SM) * sm_count();
     if (grid > items) grid = items;
+    if (schedule != nullptr) {
+        // every block of the table must be resident at once (the kernel is persistent: one block per table entry)
+        STOF_REQUIRE(schedule_blocks >= 1 && schedule_blocks <= A_CTAS_PER_SM * sm_count(),
+                     "block_attn: schedule made for %d thread blocks, this GPU runs at most %d", schedule_blocks, A_CTAS_PER_SM * sm_count());
+        STOF_REQUIRE((reinterpret_cast<uintptr_t>(schedule) & 3u) == 0, "block_attn: schedule must be 4-byte aligned");
+        grid = schedule_blocks;
+    }
     block_attn_kernel<<<static_cast<unsigned>(grid), A_THREADS, A_SMEM_BYTES, stream>>>(mq, mk, mv, mo, p);
     STOF_CUDA(cudaGetLastError());
     return STOF_OK;
+}
+
+extern "C" int stof_block_attn(const void* q, const void* k, const void* v, void* out, int batch, int heads, int seq_len, int head_dim,
+                               const long long q_strides[3], const long long k_strides[3], const long long v_strides[3],
+                               const long long out_strides[3], const int* part_row_ptr, const void* part_block_mask, const void* plan,
+                               int block_m, int block_n, int num_warps, float softmax_scale, int* status_dev, void* stream) {
+    return launch_block_attn(q, k, v, out, batch, heads, seq_len, head_dim, q_strides, k_strides, v_strides, out_strides, part_row_ptr,
+                             part_block_mask, plan, block_m, block_n, num_warps, softmax_scale, nullptr, 0, status_dev, stream);
+}
+
+extern "C" int stof_block_attn_scheduled(const void* q, const void* k, const void* v, void* out, int batch, int heads, int seq_len,
+                                         int head_dim, const long long q_strides[3], const long long k_strides[3],
+                                         const long long v_strides[3], const long long out_strides[3], const int* part_row_ptr,
+                                         const void* part_block_mask, const void* plan, int block_m, int block_n, int num_warps,
+                                         float softmax_scale, const int* schedule, int schedule_blocks, int* status_dev, void* stream) {
+    STOF_REQUIRE(schedule != nullptr, "block_attn_scheduled: null schedule");
+    return launch_block_attn(q, k, v, out, batch, heads, seq_len, head_dim, q_strides, k_strides, v_strides, out_strides, part_row_ptr,
+                             part_block_mask, plan, block_m, block_n, num_warps, softmax_scale, schedule, schedule_blocks, status_dev, stream);
 }

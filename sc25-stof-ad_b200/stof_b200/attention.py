@@ -37,6 +37,61 @@ def attention_plan(full_row_ptr, full_col_idx, part_row_ptr, part_col_idx, seq_l
     return plan
 
 
+_SCHED_CACHE = OrderedDict()
+_SCHED_OVERHEAD_STEPS = 1.5          # per-item fixed work (prologue, epilogue, pipeline refill) in units of one tile step
+_SCHED_GROUP_BH = 40                 # (batch, head) pairs whose K/V are kept together in time (L2 residency)
+
+
+def lpt_schedule(tile_counts, batch_heads: int, blocks: int):
+    """Longest-processing-time deal of the work items (query tile x (batch, head)) to `blocks` thread blocks: items in
+    descending cost (tile count + a fixed per-item overhead) each go to the block with the least work so far; inside a
+    block the items are then ordered by (batch, head) group, heaviest first.  Returns the int32 table that
+    `stof_block_attn_scheduled` takes.  Pure host code (used by `attention_schedule` and tested on the CPU)."""
+    import heapq
+    nqt = len(tile_counts)
+    cost = [float(n) + _SCHED_OVERHEAD_STEPS if n > 0 else 0.25 for n in tile_counts]
+    order = sorted(range(nqt), key=lambda t: (-cost[t], t))
+    total = nqt * batch_heads
+    blocks = max(1, min(int(blocks), total))
+    heap = [(0.0, b) for b in range(blocks)]
+    lists = [[] for _ in range(blocks)]
+    for t in order:
+        c = cost[t]
+        for bh in range(batch_heads):
+            load, b = heapq.heappop(heap)
+            lists[b].append((bh // _SCHED_GROUP_BH, -c, bh * nqt + t))
+            heapq.heappush(heap, (load + c, b))
+    table = [blocks, 0]
+    ids = []
+    for lst in lists:
+        lst.sort()
+        ids.extend(x[2] for x in lst)
+        table.append(len(ids))
+    return torch.tensor(table + ids, dtype=torch.int32), blocks
+
+
+def attention_schedule(plan, seq_len: int, batch: int, heads: int):
+    """Balanced deal of the work items for this plan and (batch, heads), cached; None when every item gets its own block.
+    The first call for a plan reads its per-tile counts back to the host (one small synchronising copy)."""
+    dev = plan.device
+    nqt = (seq_len + 127) // 128
+    blocks = 2 * torch.cuda.get_device_properties(dev).multi_processor_count
+    if nqt * batch * heads <= blocks:
+        return None, 0
+    key = (plan.data_ptr(), plan._version, seq_len, batch, heads, str(dev))
+    hit = _SCHED_CACHE.get(key)
+    if hit is not None:
+        _SCHED_CACHE.move_to_end(key)
+        return hit[0], hit[1]
+    counts = plan[32:32 + 4 * nqt].view(torch.int32).cpu().tolist()          # the plan's tile count per query tile
+    table, blocks = lpt_schedule(counts, batch * heads, blocks)
+    table = table.to(dev)
+    _SCHED_CACHE[key] = (table, blocks, plan)
+    while len(_SCHED_CACHE) > 4 * _PLAN_CACHE_MAX:
+        _SCHED_CACHE.popitem(last=False)
+    return table, blocks
+
+
 def block_attention(q, k, v, out, full_row_ptr, full_col_idx, part_row_ptr, part_col_idx, part_block_mask,
                     load_row_ptr, load_col_idx, block_m: int, block_n: int, num_warps: int = 4, softmax_scale=None):
     """Runs the attention kernel on (B,H,S,64)-shaped *views*: q, k, v and out may be arbitrary
@@ -65,13 +120,22 @@ def block_attention(q, k, v, out, full_row_ptr, full_col_idx, part_row_ptr, part
     dev = q.device
     L = _lib.lib()
     plan = attention_plan(full_row_ptr, full_col_idx, part_row_ptr, part_col_idx, S, int(block_m), int(block_n))
+    schedule, sched_blocks = attention_schedule(plan, S, B, H)
     with torch.cuda.device(dev):
         st = _lib.status_word(dev)
-        rc = L.stof_block_attn(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), B, H, S, D,
-                               _lib.strides3(q.stride()[:3]), _lib.strides3(k.stride()[:3]),
-                               _lib.strides3(v.stride()[:3]), _lib.strides3(out.stride()[:3]),
-                               _lib.ptr(part_row_ptr), _lib.ptr(part_block_mask), _lib.ptr(plan),
-                               int(block_m), int(block_n), int(num_warps), scale, _lib.ptr(st), _lib.current_stream_ptr(dev))
+        if schedule is None:
+            rc = L.stof_block_attn(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), B, H, S, D,
+                                   _lib.strides3(q.stride()[:3]), _lib.strides3(k.stride()[:3]),
+                                   _lib.strides3(v.stride()[:3]), _lib.strides3(out.stride()[:3]),
+                                   _lib.ptr(part_row_ptr), _lib.ptr(part_block_mask), _lib.ptr(plan),
+                                   int(block_m), int(block_n), int(num_warps), scale, _lib.ptr(st), _lib.current_stream_ptr(dev))
+        else:
+            rc = L.stof_block_attn_scheduled(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), B, H, S, D,
+                                             _lib.strides3(q.stride()[:3]), _lib.strides3(k.stride()[:3]),
+                                             _lib.strides3(v.stride()[:3]), _lib.strides3(out.stride()[:3]),
+                                             _lib.ptr(part_row_ptr), _lib.ptr(part_block_mask), _lib.ptr(plan),
+                                             int(block_m), int(block_n), int(num_warps), scale, _lib.ptr(schedule), int(sched_blocks),
+                                             _lib.ptr(st), _lib.current_stream_ptr(dev))
     _lib.check(rc, "stof_block_attn")
     return out
 

@@ -128,3 +128,26 @@ def test_workload_recipes_equal_the_oracle_recipes():
     g = torch.Generator().manual_seed(0)
     assert torch.equal(q, torch.randn(1, 12, 256, 64, generator=g).half())
     assert wl.attention_flops(286, 16, 12) == pytest.approx(5.758e10, rel=1e-3)
+
+
+def test_lpt_schedule_table():
+    """Host-side deal of the attention work items: every item exactly once, offsets monotone, and a better balance than
+    dealing the sorted items round-robin."""
+    from stof_b200.attention import lpt_schedule, _SCHED_OVERHEAD_STEPS
+    counts = [32, 6, 7, 9, 12, 12, 0, 11, 9, 10, 13, 8, 9, 12, 10, 11]
+    bh, blocks = 48, 40
+    table, g = lpt_schedule(counts, bh, blocks)
+    t = table.tolist()
+    assert g == blocks and t[0] == blocks and t[1] == 0 and t[1 + blocks] == len(counts) * bh
+    offs, ids = t[1:2 + blocks], t[2 + blocks:]
+    assert all(a <= b for a, b in zip(offs, offs[1:]))
+    assert sorted(ids) == list(range(len(counts) * bh))
+    cost = lambda i: (counts[i % len(counts)] + _SCHED_OVERHEAD_STEPS) if counts[i % len(counts)] else 0.25
+    loads = [sum(cost(i) for i in ids[offs[b]:offs[b + 1]]) for b in range(blocks)]
+    order = sorted(range(len(counts)), key=lambda q: -counts[q])
+    rr = [0.0] * blocks
+    for n, i in enumerate(q + len(counts) * h for q in order for h in range(bh)):
+        rr[n % blocks] += cost(i)
+    assert max(loads) <= max(rr) and max(loads) <= 1.06 * sum(loads) / blocks
+    few, g2 = lpt_schedule([3, 2], 1, 40)                     # fewer items than blocks: one block per item
+    assert g2 == 2 and few.tolist()[0] == 2

@@ -232,3 +232,36 @@ def test_host_buffer_pipeline_matches_device_operator():
         want = stof_b200.block_attention(qd, kd, vd, torch.empty_like(qd), *idx, 64, 64)
         torch.cuda.synchronize()
         assert torch.equal(out_h, want.cpu())
+
+
+@pytest.mark.gpu
+def test_scheduled_deal_gives_identical_results():
+    """More work items than resident thread blocks: `block_attention` deals them with the host-made longest-processing-time
+    table (`stof_block_attn_scheduled`); the result is bit-identical to the default round-robin deal of `stof_block_attn`,
+    and a table that names an item outside the launch is reported through the status word instead of being followed."""
+    import stof_b200
+    from stof_b200 import _lib, attention as A
+    dev = torch.device("cuda:0")
+    S, B, H = 1024, 8, 12                                     # 8 x 12 x 8 = 768 items
+    g = torch.Generator().manual_seed(5)
+    mask = torch.from_numpy(om.generate_bigbird_mask(1, S, globalwidth=64, bandwidth=96).astype(np.float16)).to(dev)
+    idx = stof_b200.get_sparse_storage(mask, 64, 64)[1:]
+    q, k, v = (torch.randn(B, H, S, 64, generator=g).half().to(dev) for _ in range(3))
+    got = stof_b200.block_attention(q, k, v, torch.empty_like(q), *idx, 64, 64)
+    plan = A.attention_plan(idx[0], idx[1], idx[2], idx[3], S, 64, 64)
+    table, blocks = A.attention_schedule(plan, S, B, H)
+    assert table is not None and blocks == table[0].item()
+    L = _lib.lib()
+    want = torch.empty_like(q)
+    st = _lib.status_word(dev)
+    args = (_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(want), B, H, S, 64, _lib.strides3(q.stride()[:3]), _lib.strides3(k.stride()[:3]),
+            _lib.strides3(v.stride()[:3]), _lib.strides3(want.stride()[:3]), _lib.ptr(idx[2]), _lib.ptr(idx[4]), _lib.ptr(plan), 64, 64, 4, 0.125)
+    assert L.stof_block_attn(*args, _lib.ptr(st), _lib.current_stream_ptr(dev)) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+    bad = table.clone()
+    bad[2 + blocks] = B * H * (S // 128) + 5                  # first item of block 0: not an item of this launch
+    assert L.stof_block_attn_scheduled(*args, _lib.ptr(bad), int(blocks), _lib.ptr(st), _lib.current_stream_ptr(dev)) == 0
+    torch.cuda.synchronize()
+    with pytest.raises(stof_b200.StofError):
+        _lib.check_status(dev, "bad schedule")
