@@ -323,7 +323,7 @@ def run_attention(args, rank, world, local):
         "cpu_baseline": {"value": cpu_val, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port", "sample": cpu_desc,
                          "seconds": cpu_s},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
-                "api": "stof_b200.block_attention_host: pinned host q/k/v in, host result out, batch chunks of 2 over three streams"},
+                "api": "stof_b200.block_attention_host: pinned host q/k/v in, host result out, four batch chunks over three streams"},
         "gpu_launches": args.steps,
         "clocks": clocks.summary(),
         "compaction": {"ms": comp_best, "mask_bytes": mask_bytes, "gbs": mask_bytes / (comp_best * 1e-3) / 1e9,

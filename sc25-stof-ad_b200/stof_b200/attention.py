@@ -224,10 +224,13 @@ _HOST_PIPELINES = {}
 
 
 def block_attention_host(q_host, k_host, v_host, out_host, full_row_ptr, full_col_idx, part_row_ptr, part_col_idx, part_block_mask,
-                         load_row_ptr, load_col_idx, block_m: int, block_n: int, num_warps: int = 4, chunk_batch: int = 2):
+                         load_row_ptr, load_col_idx, block_m: int, block_n: int, num_warps: int = 4, chunk_batch=None):
     """`block_attn_mask` for host-resident q, k, v: result in `out_host` (may be `q_host`), copies overlapped with
     the kernel by a per-device `HostAttentionPipeline`.  The block index tensors are device tensors, as for the
-    device-side operator (src/ops/package_op.py:50-74)."""
+    device-side operator (src/ops/package_op.py:50-74).  `chunk_batch` defaults to a quarter of the batch: four chunks keep
+    the copy engines busy in both directions while the per-chunk host work (copies, events, one launch) stays small."""
+    if chunk_batch is None:
+        chunk_batch = max(1, (q_host.shape[0] + 3) // 4)
     dev = full_row_ptr.device
     key = (str(dev), int(chunk_batch))
     pipe = _HOST_PIPELINES.get(key)
