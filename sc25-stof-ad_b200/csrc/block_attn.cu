@@ -7,7 +7,8 @@
 // code for each 16-row x 16-column group (0 absent, 1 full, 2+i partial tile i of the row block).
 //
 // Kernel.  Persistent, two thread blocks per SM, static schedule over the items (heavy query tiles first inside groups of
-// (batch, head) pairs small enough to keep their K/V in L2).
+// (batch, head) pairs small enough to keep their K/V in L2, dealt round-robin; or a table made by the caller that balances the
+// tile counts over the thread blocks).
 //   warp 4      TMA producer: Q tile of the next item (double-buffered), K tiles through a ring of four slots, V tiles through
 //               a ring of three
 //   warp 5      MMA issuer:   S = Q K^T (128 x 64 x 64) into one of THREE S buffers in tensor memory, up to three tiles ahead
