@@ -151,3 +151,31 @@ def test_lpt_schedule_table():
     assert max(loads) <= max(rr) and max(loads) <= 1.06 * sum(loads) / blocks
     few, g2 = lpt_schedule([3, 2], 1, 40)                     # fewer items than blocks: one block per item
     assert g2 == 2 and few.tolist()[0] == 2
+
+
+def test_util_helpers_of_the_reference_scripts(tmp_path):
+    """`util.masks.flex_*_mask`, `util.utils.{transpose_for_scores1, read_config_file, get_best_config}`: the helper names the
+    reference's benchmark scripts import, with the reference's behaviour (score-mod predicates with its constants; tuning-log
+    parser)."""
+    import torch
+    from util import masks as um, utils as uu
+    q = torch.arange(400)[:, None]
+    k = torch.arange(400)[None, :]
+    w = um.flex_sliding_window_mask(0, 0, q, k)
+    assert bool(w[300, 44]) and not bool(w[300, 43]) and bool(w[0, 399])              # q - kv <= 256, one-sided
+    lf = um.flex_longformer_mask(0, 0, q, k)
+    assert bool(lf[390, 100]) and bool(lf[100, 390 - 390]) and not bool(lf[390, 64]) and bool(lf[20, 399])
+    bb = um.flex_bigbird_mask(0, 0, q, k)
+    assert bool(bb[399, 0]) and not bool(bb[397, 64]) and torch.equal(bb, lf)      # its extra keys (key 0) are global already
+    assert um.flex_causal_mask(0, 0, 5, 5) and not um.flex_causal_mask(0, 0, 4, 5)
+    x = torch.arange(2 * 3 * 768, dtype=torch.float32).reshape(2, 3, 768)
+    assert uu.transpose_for_scores1(x).shape == (2, 12, 3, 64) and torch.equal(uu.transpose_for_scores1(x)[1, 2, 1], x[1, 1, 128:192])
+    log = tmp_path / "tuning.txt"
+    log.write_text("num_warp4 | m64n64 | bs:16 | seq:2048 | 0.52 ms/iter | Speedup/FA2: 1.93\nheader line\n"
+                   "num_warp8 | m128n64 | bs:16 | seq:2048 | 0.61 ms/iter | Speedup/FA2: 1.6\n"
+                   "num_warp2 | m32n32 | bs:1 | seq:256 | 0.02 ms/iter | Speedup/FA2: 3.1\n")
+    table = uu.read_config_file(str(log))
+    assert table == {16: {2048: [(64, 64, 4), (128, 64, 8)]}, 1: {256: [(32, 32, 2)]}}
+    assert uu.get_best_config(table, 16, 2048) == (64, 64, 4)
+    with pytest.raises(ValueError):
+        uu.get_best_config(table, 2, 2048)
