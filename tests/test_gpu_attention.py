@@ -265,3 +265,22 @@ def test_scheduled_deal_gives_identical_results():
     torch.cuda.synchronize()
     with pytest.raises(stof_b200.StofError):
         _lib.check_status(dev, "bad schedule")
+
+
+@pytest.mark.gpu
+def test_long_sequence_16384_sliding_window_with_partial_blocks():
+    """S = 16384 (eight times the largest benchmark sequence): 128 query tiles, 256 key tiles in the plan, element-granular
+    window (every block on the band is partial).  Compared with the block-index oracle, which only touches listed blocks."""
+    import stof_b200
+    dev = torch.device("cuda:0")
+    S, B, H = 16384, 1, 2
+    mask = om.generate_sliding_mask(1, S, 100, False, np.float16)
+    st = om.get_sparse_storage(mask, 64, 64)
+    idx = stof_b200.get_sparse_storage(torch.from_numpy(mask).to(dev), 64, 64)
+    assert np.array_equal(idx[7].cpu().numpy(), st.load_col_idx) and np.array_equal(idx[3].cpu().numpy(), st.part_row_ptr)
+    g = torch.Generator().manual_seed(16384)
+    q, k, v = (torch.randn(B, H, S, 64, generator=g).half() for _ in range(3))
+    got = stof_b200.block_attention(q.to(dev), k.to(dev), v.to(dev), torch.empty(B, H, S, 64, dtype=torch.float16, device=dev), *idx[1:], 64, 64)
+    torch.cuda.synchronize()
+    want = oa.block_attention_from_index(q, k, v, st, 64, 64)
+    assert (got.float().cpu() - want).abs().max().item() <= 2e-3
