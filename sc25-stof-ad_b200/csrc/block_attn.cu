@@ -99,7 +99,7 @@ plan_kernel(const int* __restrict__ full_row_ptr, const int* __restrict__ full_c
         const int p0 = part_row_ptr[rb], p1 = part_row_ptr[rb + 1];
         for (int i = p0 + threadIdx.x; i < p1; i += blockDim.x) {
             const int c = part_col_idx[i];
-            if (c >= 0 && c < ncb && i - p0 < 65534) table[lrb * ncb + c] = static_cast<uint16_t>(2 + (i - p0));
+            if (c >= 0 && c < ncb && i - p0 < 16382) table[lrb * ncb + c] = static_cast<uint16_t>(2 + (i - p0));     // 14-bit codes
             else if (status) atomicCAS(status, 0, STATUS_BAD_INDEX);
         }
     }
@@ -126,13 +126,26 @@ plan_kernel(const int* __restrict__ full_row_ptr, const int* __restrict__ full_c
     }
     __syncthreads();
     const int count = s_count;
-    // codes[j][row group 0..7][col group 0..3]
+    // codes[j][row group 0..7][col group 0..3], 14 bits each.  The top two bits of the LAST code of a row group carry the class
+    // of the softmax warp that owns it (32 rows = two row groups x four column groups): 0 every group absent, 1 every group
+    // full, 2 anything else - the kernel then needs no warp vote to pick its path.
     for (int i = threadIdx.x; i < count * 32; i += blockDim.x) {
         const int j = i >> 5, rg = (i >> 2) & 7, cg = i & 3;
         const int t = tiles[j];
         const int row = qt * A_TQ + rg * 16, col = t * A_TKV + cg * 16;
         uint16_t code = 0;
         if (row < seq_len && col < seq_len) code = table[((rg * 16) / bm) * ncb + col / bn];
+        if (cg == 3) {
+            bool all0 = true, all1 = true;
+            for (int r2 = (rg & ~1); r2 < (rg & ~1) + 2; ++r2)
+                for (int c2 = 0; c2 < 4; ++c2) {
+                    const int row2 = qt * A_TQ + r2 * 16, col2 = t * A_TKV + c2 * 16;
+                    const uint16_t k2 = (row2 < seq_len && col2 < seq_len) ? table[((r2 * 16) / bm) * ncb + col2 / bn] : uint16_t(0);
+                    all0 &= k2 == 0;
+                    all1 &= k2 == 1;
+                }
+            code = static_cast<uint16_t>(code | ((all0 ? 0u : (all1 ? 1u : 2u)) << 14));
+        }
         codes[i] = code;
     }
     // the last block orders the query tiles by descending tile count (stable)
@@ -256,7 +269,7 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 // groups get their -10000 * (1 - mask) addend.  `cx`, `cy` hold this thread's four group codes.
 __device__ __noinline__ void mask_scores_in_tmem(uint32_t t_s, uint32_t cx, uint32_t cy, const __half* part_block_mask, int part_base, int bm_shift,
                                                  int bn, int row_in_block, int col0) {
-    const unsigned code[4] = {cx & 0xFFFFu, cx >> 16, cy & 0xFFFFu, cy >> 16};
+    const unsigned code[4] = {cx & 0xFFFFu, cx >> 16, cy & 0xFFFFu, (cy >> 16) & 0x3FFFu};     // the top bits of the last code hold the warp class
 #pragma unroll 1
     for (int cg = 0; cg < 4; ++cg) {
         const unsigned c = code[cg];
@@ -536,10 +549,9 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     const int b = static_cast<int>(g % A_SBUF);
                     const uint2 cur = cw;
                     if (j + 1 < n) cw = __ldg(my_codes + (j + 1) * 8);     // 32 codes = 64 B = 8 uint2 per tile
-                    const bool all_absent = (cur.x | cur.y) == 0u;
-                    const bool all_full = cur.x == 0x00010001u && cur.y == 0x00010001u;
-                    const bool warp_absent = __all_sync(0xffffffffu, all_absent);
-                    const bool warp_full = __all_sync(0xffffffffu, all_full);
+                    // class of this warp's 32 x 64 part of the tile, put into the codes by the plan: the same value in every lane
+                    const unsigned warp_class = cur.y >> 30;
+                    const bool warp_absent = warp_class == 0u, warp_full = warp_class == 1u;
                     mbar_wait(&bars[AB_S_FULL + b], (g / A_SBUF) & 1, wctx, AB_S_FULL + b);
                     tc_fence_after();
                     uint32_t r0[32], r1[32];
