@@ -541,8 +541,6 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     continue;
                 }
                 const uint2* my_codes = item_codes(cur_item);
-                const uint16_t* tl = plan_tiles + static_cast<size_t>(cur_item.qt) * p.max_tiles;
-                const int row_in_block = row & (p.bm - 1);
                 float m_ref = -INFINITY, l_sum = 0.f;
 
                 for (int j = 0; j < n; ++j, ++g) {
@@ -560,8 +558,9 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                         for (int i = 0; i < 32; ++i) r0[i] = 0u;
                     } else {
                         if (!warp_full)
-                            mask_scores_in_tmem(t_lane + A_COL_S + b * A_TKV, cur.x, cur.y, p.part_block_mask, part_base, p.bm_shift, p.bn, row_in_block,
-                                                static_cast<int>(tl[j]) * A_TKV);
+                            mask_scores_in_tmem(t_lane + A_COL_S + b * A_TKV, cur.x, cur.y, p.part_block_mask, part_base, p.bm_shift, p.bn,
+                                                (cur_item.qt * A_TQ + lr) & (p.bm - 1),
+                                                static_cast<int>(plan_tiles[static_cast<size_t>(cur_item.qt) * p.max_tiles + j]) * A_TKV);
                         tmem_ld32(t_lane + A_COL_S + b * A_TKV, r0);
                         tmem_ld32(t_lane + A_COL_S + b * A_TKV + 32, r1);
                         tc_wait_ld();
