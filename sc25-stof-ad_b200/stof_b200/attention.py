@@ -70,9 +70,10 @@ def lpt_schedule(tile_counts, batch_heads: int, blocks: int):
     return torch.tensor(table + ids, dtype=torch.int32), blocks
 
 
-def attention_schedule(plan, seq_len: int, batch: int, heads: int):
-    """Balanced deal of the work items for this plan and (batch, heads), cached; None when every item gets its own block.
-    The first call for a plan reads its per-tile counts back to the host (one small synchronising copy)."""
+def attention_schedule(plan, seq_len: int, batch: int, heads: int, eager: bool = False):
+    """Balanced deal of the work items for this plan and (batch, heads), cached; None when every item gets its own block
+    and, unless `eager`, on the first use of a plan (the table is built at the second use: it costs a small synchronising
+    read of the plan's per-tile counts and a few milliseconds of host work)."""
     dev = plan.device
     nqt = (seq_len + 127) // 128
     blocks = 2 * torch.cuda.get_device_properties(dev).multi_processor_count
@@ -82,7 +83,18 @@ def attention_schedule(plan, seq_len: int, batch: int, heads: int):
     hit = _SCHED_CACHE.get(key)
     if hit is not None:
         _SCHED_CACHE.move_to_end(key)
+        if hit[0] is None:                                   # second use of this plan and shape: now the table pays off
+            counts = plan[32:32 + 4 * nqt].view(torch.int32).cpu().tolist()
+            table, blocks = lpt_schedule(counts, batch * heads, blocks)
+            hit = _SCHED_CACHE[key] = (table.to(dev), blocks, plan)
         return hit[0], hit[1]
+    if not eager:
+        # first use: an index that is used once (a caller-supplied row mask, a test) is not worth a host read and a few
+        # milliseconds of host work; remember it and run the default deal
+        _SCHED_CACHE[key] = (None, 0, plan)
+        while len(_SCHED_CACHE) > 4 * _PLAN_CACHE_MAX:
+            _SCHED_CACHE.popitem(last=False)
+        return None, 0
     counts = plan[32:32 + 4 * nqt].view(torch.int32).cpu().tolist()          # the plan's tile count per query tile
     table, blocks = lpt_schedule(counts, batch * heads, blocks)
     table = table.to(dev)

@@ -247,9 +247,12 @@ def test_scheduled_deal_gives_identical_results():
     mask = torch.from_numpy(om.generate_bigbird_mask(1, S, globalwidth=64, bandwidth=96).astype(np.float16)).to(dev)
     idx = stof_b200.get_sparse_storage(mask, 64, 64)[1:]
     q, k, v = (torch.randn(B, H, S, 64, generator=g).half().to(dev) for _ in range(3))
-    got = stof_b200.block_attention(q, k, v, torch.empty_like(q), *idx, 64, 64)
+    first = stof_b200.block_attention(q, k, v, torch.empty_like(q), *idx, 64, 64)      # first use of the plan: default deal
+    got = stof_b200.block_attention(q, k, v, torch.empty_like(q), *idx, 64, 64)        # second use: the host-made table
+    assert torch.equal(first, got)
     plan = A.attention_plan(idx[0], idx[1], idx[2], idx[3], S, 64, 64)
-    table, blocks = A.attention_schedule(plan, S, B, H)
+    assert A._SCHED_CACHE[(plan.data_ptr(), plan._version, S, B, H, str(plan.device))][0] is not None
+    table, blocks = A.attention_schedule(plan, S, B, H, eager=True)
     assert table is not None and blocks == table[0].item()
     L = _lib.lib()
     want = torch.empty_like(q)
