@@ -105,6 +105,30 @@ class BertEncoder:
 
     __call__ = forward
 
+    def capture(self, hidden: torch.Tensor):
+        """Records one forward pass on `hidden` (a tensor the caller keeps and refills in place) into a CUDA graph and returns
+        `replay() -> output tensor` (the output buffer is reused by every replay).  Two eager passes run first so that every
+        buffer, the attention plan and its balanced schedule exist: a captured pass allocates nothing and reads nothing back.
+        All launches of a pass then cost one graph launch on the host."""
+        if not hidden.is_cuda:
+            raise _lib.StofError("capture: hidden must live on the GPU")
+        dev = hidden.device
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            self.forward(hidden)
+            self.forward(hidden)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            out = self.forward(hidden)
+
+        def replay():
+            graph.replay()
+            return out
+        replay.graph = graph
+        return replay
+
 
 def gpt2_stack(layers: List[EncoderWeights], head_num: int, eps: float = 1e-5, block_m: int = 64, block_n: int = 64) -> BertEncoder:
     """The reference's GPT-2 loop (src/benchmk_end2end.py:93-147): the same post-LN layer with the tanh-form GELU;

@@ -208,3 +208,23 @@ def test_encoder_config5_shapes_batch_independence():
     want = of.bert_layer(hidden[:1], params[0], torch.from_numpy(mask.astype(np.float32)), heads, eps=1e-12)
     rows = torch.arange(0, S, 37)
     assert _err(got[:, rows], want[:, rows]) <= 2e-3 * max(1.0, want.abs().max().item())
+
+
+def test_encoder_forward_captured_in_a_cuda_graph():
+    """`BertEncoder.capture`: a replayed graph of the forward pass gives the eager result, also after the input buffer has
+    been refilled in place."""
+    import stof_b200
+    B, S, hid, heads, ffn = 2, 512, 256, 4, 1024
+    params = of.make_bert_params(hid, ffn, 2, seed=41, random_affine=True)
+    enc = stof_b200.BertEncoder([stof_b200.EncoderWeights.from_dict(p, "cuda") for p in params], head_num=heads, eps=1e-12)
+    enc.set_mask(torch.from_numpy(om.generate_sliding_mask(1, S, 100, False, np.float16)).cuda())
+    x = _rand((B, S, hid), 42).cuda()
+    eager = enc(x).clone()
+    replay = enc.capture(x)
+    assert torch.equal(replay(), eager)
+    x2 = _rand((B, S, hid), 43).cuda()
+    want2 = enc(x2).clone()
+    x.copy_(x2)
+    assert torch.equal(replay(), want2)
+    from stof_b200 import _lib
+    _lib.check_status(x.device, "graph replay")
