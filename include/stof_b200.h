@@ -117,6 +117,20 @@ int stof_block_attn_plan(const int* full_row_ptr, const int* full_col_idx,
                          int seq_len, int block_m, int block_n,
                          void* plan, size_t plan_bytes, int* status_dev, void* stream);
 
+/* The same plan with the query tiles put together by the caller.  No counterpart in the reference
+ * (its kernel works on one BLOCK_M row block per thread block).  The kernel's 128-row query tile is
+ * two 64-row halves of the sequence, halves 2t and 2t + 1 in the plan above.  Here `pairs` (device,
+ * 2 ints per query tile, ceil(seq_len / 128) tiles) names the two halves of every tile by their index
+ * seq_row / 64; the second may be -1.  A caller pairs halves whose lists of key tiles agree (rows r
+ * and r + 2 of a dilated mask, say), which spares the tensor core and half of the softmax warps the
+ * key tiles that only one half of a default tile lists.  Every half must appear in exactly one tile:
+ * a half that is left out is never written, which the plan does not check; an index outside
+ * [0, ceil(seq_len / 64)) sets *status_dev and the tile falls back to half 0 alone. */
+int stof_block_attn_plan_paired(const int* full_row_ptr, const int* full_col_idx,
+                                const int* part_row_ptr, const int* part_col_idx, const int* pairs,
+                                int seq_len, int block_m, int block_n,
+                                void* plan, size_t plan_bytes, int* status_dev, void* stream);
+
 int stof_block_attn(const void* q, const void* k, const void* v, void* out,
                     int batch, int heads, int seq_len, int head_dim,
                     const long long q_strides[3], const long long k_strides[3],

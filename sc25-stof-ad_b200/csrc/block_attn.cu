@@ -66,19 +66,38 @@ __host__ __device__ inline size_t plan_off_tiles(int nqt) { return plan_off_orde
 __host__ __device__ inline size_t plan_off_codes(int nqt, int maxt) {
     return plan_off_tiles(nqt) + ((static_cast<size_t>(nqt) * maxt * 2 + 15) & ~static_cast<size_t>(15));
 }
-__host__ __device__ inline size_t plan_total_bytes(int nqt, int maxt) { return plan_off_codes(nqt, maxt) + static_cast<size_t>(nqt) * maxt * 64; }
+// first sequence row of the two 64-row halves of each query tile (int2; y = -1 when the tile has one half only)
+__host__ __device__ inline size_t plan_off_halves(int nqt, int maxt) { return plan_off_codes(nqt, maxt) + static_cast<size_t>(nqt) * maxt * 64; }
+__host__ __device__ inline size_t plan_total_bytes(int nqt, int maxt) {
+    return plan_off_halves(nqt, maxt) + ((static_cast<size_t>(nqt) * 8 + 15) & ~static_cast<size_t>(15));
+}
 
 // One thread block per query tile: code table in shared memory -> ordered tile list + 8x4 group codes per tile.
+// A query tile is two 64-row halves of the sequence: halves 2t and 2t + 1 by default, or the two that `pairs` names for
+// it (a caller pairs halves whose key tile lists agree, so that fewer warps idle on tiles only one half lists).
 // The last block to finish ranks the query tiles by tile count (descending, stable) for the scheduler.
 __global__ void __launch_bounds__(256)
 plan_kernel(const int* __restrict__ full_row_ptr, const int* __restrict__ full_col_idx, const int* __restrict__ part_row_ptr,
-            const int* __restrict__ part_col_idx, int seq_len, int bm, int bn, unsigned char* plan, unsigned int* ticket, int* status) {
-    extern __shared__ uint16_t table[];                 // [nrb][ncb]
+            const int* __restrict__ part_col_idx, const int2* __restrict__ pairs, int seq_len, int bm, int bn, unsigned char* plan,
+            unsigned int* ticket, int* status) {
+    extern __shared__ uint16_t table[];                 // [2 halves x row blocks per half][ncb]
     __shared__ int s_count;
     __shared__ bool s_last;
     const int nqt = gridDim.x, maxt = (seq_len + A_TKV - 1) / A_TKV;
     const int qt = blockIdx.x;
-    const int nbm = seq_len / bm, ncb = seq_len / bn, nrb = A_TQ / bm;
+    const int nbm = seq_len / bm, ncb = seq_len / bn;
+    const int nrbh = bm >= 64 ? 1 : 64 / bm, nrb = 2 * nrbh;        // table rows per half, per tile
+    const int n_half = (seq_len + 63) / 64;
+    int half[2] = {2 * qt, 2 * qt + 1 < n_half ? 2 * qt + 1 : -1};
+    if (pairs != nullptr) {
+        const int2 pr = pairs[qt];
+        if (pr.x >= 0 && pr.x < n_half && pr.y >= -1 && pr.y < n_half && pr.x != pr.y) {
+            half[0] = pr.x; half[1] = pr.y;
+        } else {
+            if (status && threadIdx.x == 0) atomicCAS(status, 0, STATUS_BAD_INDEX);
+            half[0] = 0; half[1] = -1;
+        }
+    }
     int* n_tiles = reinterpret_cast<int*>(plan + plan_off_ntiles());
     int2* order = reinterpret_cast<int2*>(plan + plan_off_order(nqt));     // per rank: {query tile, tile count}
     uint16_t* tiles = reinterpret_cast<uint16_t*>(plan + plan_off_tiles(nqt)) + static_cast<size_t>(qt) * maxt;
@@ -88,8 +107,10 @@ plan_kernel(const int* __restrict__ full_row_ptr, const int* __restrict__ full_c
     for (int i = threadIdx.x; i < nrb * ncb; i += blockDim.x) table[i] = 0;
     __syncthreads();
     for (int lrb = 0; lrb < nrb; ++lrb) {
-        const int rb = qt * nrb + lrb;
-        if (rb >= nbm) break;
+        const int hb = half[lrb / nrbh];
+        if (hb < 0) continue;
+        const int rb = bm >= 64 ? (hb * 64) / bm : hb * nrbh + lrb % nrbh;
+        if (rb >= nbm) continue;
         const int f0 = full_row_ptr[rb], f1 = full_row_ptr[rb + 1];
         for (int i = f0 + threadIdx.x; i < f1; i += blockDim.x) {
             const int c = full_col_idx[i];
@@ -129,18 +150,21 @@ plan_kernel(const int* __restrict__ full_row_ptr, const int* __restrict__ full_c
     // codes[j][row group 0..7][col group 0..3], 14 bits each.  The top two bits of the LAST code of a row group carry the class
     // of the softmax warp that owns it (32 rows = two row groups x four column groups): 0 every group absent, 1 every group
     // full, 2 anything else - the kernel then needs no warp vote to pick its path.
+    // sequence row of 16-row group rg of this tile (-1: none), and its row of the table
+    auto group_row = [&](int rg) { return half[rg >> 2] < 0 ? -1 : half[rg >> 2] * 64 + (rg & 3) * 16; };
+    auto table_row = [&](int rg) { return (rg >> 2) * nrbh + (bm >= 64 ? 0 : ((rg & 3) * 16) / bm); };
     for (int i = threadIdx.x; i < count * 32; i += blockDim.x) {
         const int j = i >> 5, rg = (i >> 2) & 7, cg = i & 3;
         const int t = tiles[j];
-        const int row = qt * A_TQ + rg * 16, col = t * A_TKV + cg * 16;
+        const int row = group_row(rg), col = t * A_TKV + cg * 16;
         uint16_t code = 0;
-        if (row < seq_len && col < seq_len) code = table[((rg * 16) / bm) * ncb + col / bn];
+        if (row >= 0 && row < seq_len && col < seq_len) code = table[table_row(rg) * ncb + col / bn];
         if (cg == 3) {
             bool all0 = true, all1 = true;
             for (int r2 = (rg & ~1); r2 < (rg & ~1) + 2; ++r2)
                 for (int c2 = 0; c2 < 4; ++c2) {
-                    const int row2 = qt * A_TQ + r2 * 16, col2 = t * A_TKV + c2 * 16;
-                    const uint16_t k2 = (row2 < seq_len && col2 < seq_len) ? table[((r2 * 16) / bm) * ncb + col2 / bn] : uint16_t(0);
+                    const int row2 = group_row(r2), col2 = t * A_TKV + c2 * 16;
+                    const uint16_t k2 = (row2 >= 0 && row2 < seq_len && col2 < seq_len) ? table[table_row(r2) * ncb + col2 / bn] : uint16_t(0);
                     all0 &= k2 == 0;
                     all1 &= k2 == 1;
                 }
@@ -148,6 +172,8 @@ plan_kernel(const int* __restrict__ full_row_ptr, const int* __restrict__ full_c
         }
         codes[i] = code;
     }
+    if (threadIdx.x == 0)
+        reinterpret_cast<int2*>(plan + plan_off_halves(nqt, maxt))[qt] = make_int2(half[0] * 64, half[1] < 0 ? -1 : half[1] * 64);
     // the last block orders the query tiles by descending tile count (stable)
     __threadfence();
     __syncthreads();
@@ -218,14 +244,24 @@ struct Item {
     int qt, head, batch, n;
     bool valid;
 };
-__device__ __forceinline__ Item fetch_item(unsigned k, const AttnParams& p, const int2* sched) {
-    Item it;
-    it.qt = 0; it.head = 0; it.batch = 0; it.n = 0;
+// Step one of fetching item k of this thread block: its raw number (A_NO_ITEM when the block has no k-th item).
+constexpr unsigned A_NO_ITEM = 0xffffffffu;
+__device__ __forceinline__ unsigned fetch_item_id(unsigned k, const AttnParams& p) {
     if (p.schedule != nullptr) {
         const int b0 = __ldg(p.schedule + 1 + blockIdx.x), b1 = __ldg(p.schedule + 2 + blockIdx.x);
-        it.valid = static_cast<long long>(k) < static_cast<long long>(b1) - b0;
-        if (!it.valid) return it;
-        const unsigned id = static_cast<unsigned>(__ldg(p.schedule + 2 + gridDim.x + b0 + static_cast<int>(k)));
+        if (static_cast<long long>(k) >= static_cast<long long>(b1) - b0) return A_NO_ITEM;
+        return static_cast<unsigned>(__ldg(p.schedule + 2 + gridDim.x + b0 + static_cast<int>(k)));
+    }
+    const unsigned idx = blockIdx.x + k * gridDim.x;
+    return idx < p.total_items ? idx : A_NO_ITEM;
+}
+// Step two: the item's coordinates and its tile count.
+__device__ __forceinline__ Item decode_item(unsigned id, const AttnParams& p, const int2* sched) {
+    Item it;
+    it.qt = 0; it.head = 0; it.batch = 0; it.n = 0;
+    it.valid = id != A_NO_ITEM;
+    if (!it.valid) return it;
+    if (p.schedule != nullptr) {
         if (id >= p.total_items) {                       // a table that does not belong to this launch: stop, and say so
             if (p.status) atomicCAS(p.status, 0, STATUS_BAD_INDEX);
             it.valid = false;
@@ -238,12 +274,9 @@ __device__ __forceinline__ Item fetch_item(unsigned k, const AttnParams& p, cons
         it.head = static_cast<int>(bh - it.batch * p.heads);
         return it;
     }
-    const unsigned idx = blockIdx.x + k * gridDim.x;
-    it.valid = idx < p.total_items;
-    if (!it.valid) return it;
     const unsigned group_items = static_cast<unsigned>(A_GROUP_BH) * p.n_qtiles;
-    const unsigned g = idx / group_items;
-    const unsigned r = idx - g * group_items;
+    const unsigned g = id / group_items;
+    const unsigned r = id - g * group_items;
     const unsigned bh0 = g * A_GROUP_BH;
     const unsigned gsize = min(static_cast<unsigned>(A_GROUP_BH), p.bh_total - bh0);     // the tail group is smaller
     const unsigned rank = r / gsize;
@@ -254,6 +287,9 @@ __device__ __forceinline__ Item fetch_item(unsigned k, const AttnParams& p, cons
     it.batch = static_cast<int>(bh / p.heads);
     it.head = static_cast<int>(bh - it.batch * p.heads);
     return it;
+}
+__device__ __forceinline__ Item fetch_item(unsigned k, const AttnParams& p, const int2* sched) {
+    return decode_item(fetch_item_id(k, p), p, sched);
 }
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
@@ -333,6 +369,7 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const int2* plan_sched = reinterpret_cast<const int2*>(p.plan + plan_off_order(p.n_qtiles));
     const uint16_t* plan_tiles = reinterpret_cast<const uint16_t*>(p.plan + plan_off_tiles(p.n_qtiles));
     const uint16_t* plan_codes = reinterpret_cast<const uint16_t*>(p.plan + plan_off_codes(p.n_qtiles, p.max_tiles));
+    const int2* plan_halves = reinterpret_cast<const int2*>(p.plan + plan_off_halves(p.n_qtiles, p.max_tiles));
 
     if (threadIdx.x == 0) {
         *abort_flag = (p.status != nullptr && *p.status != 0) ? 1 : 0;
@@ -394,9 +431,14 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     if (kc.j == 0) {
                         const int qb = kc.it & 1;
                         mbar_wait(&bars[AB_Q_EMPTY + qb], static_cast<uint32_t>(((kc.it >> 1) & 1) ^ 1), wctx, AB_Q_EMPTY + qb);
-                        mbar_arrive_expect_tx(&bars[AB_Q_FULL + qb], A_Q_BYTES);
-                        tma_tile(q_smem + qb * A_Q_BYTES, &map_q, &bars[AB_Q_FULL + qb], kc.item.qt * A_TQ, kc.item.head, kc.item.batch, p.slot_s[0],
+                        // the tile's two 64-row halves (the second may be missing; its rows then carry "absent" codes only)
+                        const int2 hr = __ldg(plan_halves + kc.item.qt);
+                        mbar_arrive_expect_tx(&bars[AB_Q_FULL + qb], hr.y >= 0 ? A_Q_BYTES : A_Q_BYTES / 2);
+                        tma_tile(q_smem + qb * A_Q_BYTES, &map_q, &bars[AB_Q_FULL + qb], hr.x, kc.item.head, kc.item.batch, p.slot_s[0],
                                  p.slot_h[0], p.slot_b[0]);
+                        if (hr.y >= 0)
+                            tma_tile(q_smem + qb * A_Q_BYTES + A_Q_BYTES / 2, &map_q, &bars[AB_Q_FULL + qb], hr.y, kc.item.head, kc.item.batch,
+                                     p.slot_s[0], p.slot_h[0], p.slot_b[0]);
                     }
                     const int sl = static_cast<int>(uk % A_KSLOTS);
                     mbar_wait(&bars[AB_K_EMPTY + sl], ((uk / A_KSLOTS) & 1) ^ 1, wctx, AB_K_EMPTY + sl);
@@ -494,9 +536,13 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             const float scale = p.scale_log2, inv_scale = 1.0f / p.scale_log2;
             unsigned g = 0;                                  // steps of this block so far (matches the MMA warp's count)
             // per-item values that need global loads are fetched one item ahead (no dependent-load chain at item boundaries)
-            auto item_row_base = [&](const Item& x) -> int {
-                const int r = x.qt * A_TQ + lr;
-                return (x.valid && x.n > 0 && r < p.seq_len) ? __ldg(p.part_row_ptr + (r >> p.bm_shift)) : 0;
+            // first sequence row of the 64-row half this warp works on (-1: the tile has no such half)
+            auto item_half = [&](const Item& x) -> int {
+                return x.valid ? __ldg(reinterpret_cast<const int*>(plan_halves) + 2 * x.qt + (warp >> 1)) : -1;
+            };
+            auto item_row_base = [&](const Item& x, int half_row) -> int {
+                const int r = half_row + (lr & 63);
+                return (x.valid && x.n > 0 && half_row >= 0 && r < p.seq_len) ? __ldg(p.part_row_ptr + (r >> p.bm_shift)) : 0;
             };
             auto item_codes = [&](const Item& x) -> const uint2* {
                 return reinterpret_cast<const uint2*>(plan_codes + (static_cast<size_t>(x.qt) * p.max_tiles) * 32 + rg * 4);
@@ -504,7 +550,8 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             unsigned char* slab = o_smem + warp * A_OSTAGE_BYTES;       // this warp's 32 x 128 B output staging (1024-aligned)
             // writes one fp16 output row (8 x 16 B) into the slab in the 128-byte-swizzled layout of the output tensor map,
             // then one lane hands the slab to the TMA store; rows beyond the sequence end are clipped by the tensor map
-            auto store_rows = [&](const uint4 (&u)[8], const Item& x) {
+            auto store_rows = [&](const uint4 (&u)[8], const Item& x, int half_row) {
+                if (half_row < 0) return;                                // same in every lane of the warp
                 if (lane == 0) tma_store_wait_read();                    // the previous store has finished reading the slab
                 __syncwarp();
 #pragma unroll
@@ -512,32 +559,35 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
-                    tma_tile_store(&map_o, slab, x.qt * A_TQ + warp * 32, x.head, x.batch, p.slot_s[3], p.slot_h[3], p.slot_b[3]);
+                    tma_tile_store(&map_o, slab, half_row + (warp & 1) * 32, x.head, x.batch, p.slot_s[3], p.slot_h[3], p.slot_b[3]);
                     tma_store_commit();
                 }
             };
-            // two-deep item pipeline: the schedule entry of item k+2 and the row-dependent loads of item k+1 are in flight
-            // while item k is processed
+            // two-deep item pipeline: the schedule entry and half row of item k+2 and the row-dependent loads of item k+1 are
+            // in flight while item k is processed
             Item item = fetch_item(0, p, plan_sched);
             Item item2 = fetch_item(1, p, plan_sched);
-            int part_base_next = item_row_base(item);
+            int half_next = item_half(item), half2 = item_half(item2);
+            int part_base_next = item_row_base(item, half_next);
             uint2 cw_next = (item.valid && item.n > 0) ? __ldg(item_codes(item)) : make_uint2(0u, 0u);
             for (unsigned k = 0; item.valid; ++k) {
                 const Item cur_item = item;
                 const int part_base = part_base_next;
                 uint2 cw = cw_next;                              // codes of tile 0
+                const int half_row = half_next;
                 item = item2;
-                part_base_next = item_row_base(item);
+                half_next = half2;
+                part_base_next = item_row_base(item, half_next);
                 cw_next = (item.valid && item.n > 0) ? __ldg(item_codes(item)) : make_uint2(0u, 0u);
                 item2 = fetch_item(k + 2, p, plan_sched);
+                half2 = item_half(item2);
 
                 const int n = cur_item.n;
-                const int row = cur_item.qt * A_TQ + lr;
                 if (n == 0) {
                     uint4 z[8];
 #pragma unroll
                     for (int c = 0; c < 8; ++c) z[c] = make_uint4(0u, 0u, 0u, 0u);
-                    store_rows(z, cur_item);
+                    store_rows(z, cur_item, half_row);
                     continue;
                 }
                 const uint2* my_codes = item_codes(cur_item);
@@ -559,7 +609,7 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     } else {
                         if (!warp_full)
                             mask_scores_in_tmem(t_lane + A_COL_S + b * A_TKV, cur.x, cur.y, p.part_block_mask, part_base, p.bm_shift, p.bn,
-                                                (cur_item.qt * A_TQ + lr) & (p.bm - 1),
+                                                (half_row + (lr & 63)) & (p.bm - 1),
                                                 static_cast<int>(plan_tiles[static_cast<size_t>(cur_item.qt) * p.max_tiles + j]) * A_TKV);
                         tmem_ld32(t_lane + A_COL_S + b * A_TKV, r0);
                         tmem_ld32(t_lane + A_COL_S + b * A_TKV + 32, r1);
@@ -653,7 +703,7 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                             u[c].z = pack_half2(__uint_as_float(src[4]) * inv, __uint_as_float(src[5]) * inv);
                             u[c].w = pack_half2(__uint_as_float(src[6]) * inv, __uint_as_float(src[7]) * inv);
                         }
-                        store_rows(u, cur_item);
+                        store_rows(u, cur_item, half_row);
                     }
                 }
             }
@@ -697,13 +747,18 @@ int log2_exact(int v) {
     return s;
 }
 
+// shared memory of the plan kernel: one 16-bit code per (row block of either half, column block)
+size_t plan_table_bytes(int seq_len, int block_m, int block_n) {
+    return static_cast<size_t>(2 * (block_m >= 64 ? 1 : 64 / block_m)) * (seq_len / block_n) * 2;
+}
+
 int check_blocks(int seq_len, int block_m, int block_n) {
     STOF_REQUIRE(seq_len > 0, "block_attn: bad seq_len");
     STOF_REQUIRE(block_m == 16 || block_m == 32 || block_m == 64 || block_m == 128, "block_attn: BLOCK_M %d not in {16,32,64,128}", block_m);
     STOF_REQUIRE(block_n == 16 || block_n == 32 || block_n == 64 || block_n == 128, "block_attn: BLOCK_N %d not in {16,32,64,128}", block_n);
     STOF_REQUIRE(seq_len % block_m == 0 && seq_len % block_n == 0, "block_attn: seq_len %d not a multiple of BLOCK_M %d / BLOCK_N %d", seq_len,
                  block_m, block_n);
-    const size_t table_bytes = static_cast<size_t>(A_TQ / block_m) * (seq_len / block_n) * 2;
+    const size_t table_bytes = plan_table_bytes(seq_len, block_m, block_n);
     if (table_bytes > A_MAX_TABLE_BYTES) {
         set_error("block_attn: seq_len %d with %dx%d blocks needs a %zu-byte block table, beyond the maximum of %d", seq_len, block_m, block_n,
                   table_bytes, A_MAX_TABLE_BYTES);
@@ -724,8 +779,8 @@ extern "C" size_t stof_block_attn_plan_bytes(int seq_len, int block_m, int block
     return plan_total_bytes(nqt, maxt) + 16;          // trailing 16 bytes: the ticket of the plan kernel
 }
 
-extern "C" int stof_block_attn_plan(const int* full_row_ptr, const int* full_col_idx, const int* part_row_ptr, const int* part_col_idx,
-                                    int seq_len, int block_m, int block_n, void* plan, size_t plan_bytes, int* status_dev, void* stream_) {
+static int launch_plan(const int* full_row_ptr, const int* full_col_idx, const int* part_row_ptr, const int* part_col_idx, const int* pairs,
+                       int seq_len, int block_m, int block_n, void* plan, size_t plan_bytes, int* status_dev, void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (int rc = check_blocks(seq_len, block_m, block_n)) return rc;
     STOF_REQUIRE(full_row_ptr && part_row_ptr && plan, "block_attn_plan: null pointer");
@@ -740,7 +795,7 @@ extern "C" int stof_block_attn_plan(const int* full_row_ptr, const int* full_col
     unsigned int* ticket = reinterpret_cast<unsigned int*>(pl + plan_total_bytes(nqt, maxt));
     STOF_CUDA(cudaMemsetAsync(pl, 0, sizeof(PlanHeader), stream));
     STOF_CUDA(cudaMemsetAsync(ticket, 0, 16, stream));
-    const size_t smem = static_cast<size_t>(A_TQ / block_m) * (seq_len / block_n) * 2;
+    const size_t smem = plan_table_bytes(seq_len, block_m, block_n);
     static bool configured[64] = {};
     int dev = 0;
     STOF_CUDA(cudaGetDevice(&dev));
@@ -748,9 +803,25 @@ extern "C" int stof_block_attn_plan(const int* full_row_ptr, const int* full_col
         STOF_CUDA(cudaFuncSetAttribute(plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, A_MAX_TABLE_BYTES));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    plan_kernel<<<nqt, 256, smem, stream>>>(full_row_ptr, full_col_idx, part_row_ptr, part_col_idx, seq_len, block_m, block_n, pl, ticket, status_dev);
+    plan_kernel<<<nqt, 256, smem, stream>>>(full_row_ptr, full_col_idx, part_row_ptr, part_col_idx, reinterpret_cast<const int2*>(pairs), seq_len,
+                                            block_m, block_n, pl, ticket, status_dev);
     STOF_CUDA(cudaGetLastError());
     return STOF_OK;
+}
+
+extern "C" int stof_block_attn_plan(const int* full_row_ptr, const int* full_col_idx, const int* part_row_ptr, const int* part_col_idx,
+                                    int seq_len, int block_m, int block_n, void* plan, size_t plan_bytes, int* status_dev, void* stream) {
+    return launch_plan(full_row_ptr, full_col_idx, part_row_ptr, part_col_idx, nullptr, seq_len, block_m, block_n, plan, plan_bytes, status_dev,
+                       stream);
+}
+
+extern "C" int stof_block_attn_plan_paired(const int* full_row_ptr, const int* full_col_idx, const int* part_row_ptr, const int* part_col_idx,
+                                           const int* pairs, int seq_len, int block_m, int block_n, void* plan, size_t plan_bytes,
+                                           int* status_dev, void* stream) {
+    STOF_REQUIRE(pairs != nullptr, "block_attn_plan_paired: null pairs");
+    STOF_REQUIRE((reinterpret_cast<uintptr_t>(pairs) & 7u) == 0, "block_attn_plan_paired: pairs must be 8-byte aligned");
+    return launch_plan(full_row_ptr, full_col_idx, part_row_ptr, part_col_idx, pairs, seq_len, block_m, block_n, plan, plan_bytes, status_dev,
+                       stream);
 }
 
 static int launch_block_attn(const void* q, const void* k, const void* v, void* out, int batch, int heads, int seq_len, int head_dim,
@@ -791,7 +862,7 @@ static int launch_block_attn(const void* q, const void* k, const void* v, void* 
     p.bh_total = static_cast<unsigned>(batch) * static_cast<unsigned>(heads);
     CUtensorMap mq, mk, mv, mo;
     if (int rc = make_qkv_map(&mo, out, batch, heads, seq_len, out_strides, 32, &p.slot_s[3], &p.slot_h[3], &p.slot_b[3])) return rc;
-    if (int rc = make_qkv_map(&mq, q, batch, heads, seq_len, q_strides, A_TQ, &p.slot_s[0], &p.slot_h[0], &p.slot_b[0])) return rc;
+    if (int rc = make_qkv_map(&mq, q, batch, heads, seq_len, q_strides, A_TQ / 2, &p.slot_s[0], &p.slot_h[0], &p.slot_b[0])) return rc;
     if (int rc = make_qkv_map(&mk, k, batch, heads, seq_len, k_strides, A_TKV, &p.slot_s[1], &p.slot_h[1], &p.slot_b[1])) return rc;
     if (int rc = make_qkv_map(&mv, v, batch, heads, seq_len, v_strides, A_TKV, &p.slot_s[2], &p.slot_h[2], &p.slot_b[2])) return rc;
 

@@ -12,7 +12,7 @@ STOF_DTYPE_F16, STOF_DTYPE_F32 = 0, 1
 EPI_BIAS, EPI_BIAS_GELU_ERF, EPI_BIAS_GELU_TANH, EPI_BIAS_RESIDUAL, EPI_BIAS_RELU = 0, 1, 2, 3, 4
 
 EXPORTS = ("stof_version", "stof_last_error", "stof_mask_workspace_bytes", "stof_mask_classify", "stof_mask_fill", "stof_mask_compact_static",
-           "stof_block_attn_plan_bytes", "stof_block_attn_plan", "stof_block_attn", "stof_block_attn_scheduled", "stof_gemm_bias_act", "stof_bias_residual_layernorm")
+           "stof_block_attn_plan_bytes", "stof_block_attn_plan", "stof_block_attn_plan_paired", "stof_block_attn", "stof_block_attn_scheduled", "stof_gemm_bias_act", "stof_bias_residual_layernorm")
 
 
 class StofError(RuntimeError):
@@ -52,6 +52,8 @@ def lib() -> ctypes.CDLL:
     L.stof_block_attn_plan_bytes.argtypes = [i32, i32, i32]
     L.stof_block_attn_plan.restype = i32
     L.stof_block_attn_plan.argtypes = [vp, vp, vp, vp, i32, i32, i32, vp, sz, vp, vp]
+    L.stof_block_attn_plan_paired.restype = i32
+    L.stof_block_attn_plan_paired.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, vp, sz, vp, vp]
     L.stof_block_attn.restype = i32
     L.stof_block_attn.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i64x3, i64x3, i64x3, i64x3,
                                   vp, vp, vp, i32, i32, i32, f32, vp, vp]

@@ -13,27 +13,129 @@ _PLAN_CACHE = OrderedDict()
 _PLAN_CACHE_MAX = 16
 
 
-def attention_plan(full_row_ptr, full_col_idx, part_row_ptr, part_col_idx, seq_len: int, block_m: int, block_n: int):
-    """Kernel-side plan of a block index (`stof_block_attn_plan`), cached per index: the key holds the four
-    index tensors themselves (their storage cannot be recycled while the entry lives) and their versions."""
-    tensors = (full_row_ptr, full_col_idx, part_row_ptr, part_col_idx)
-    key = tuple((t.data_ptr(), t._version, t.numel()) for t in tensors) + (seq_len, block_m, block_n, str(full_row_ptr.device))
-    hit = _PLAN_CACHE.get(key)
-    if hit is not None:
-        _PLAN_CACHE.move_to_end(key)
-        return hit[0]
+_PAIR_MIN_GAIN = 0.08                # pair the halves only when that spares at least this share of the tile steps
+_HOT_PLANS = set()                   # data pointers of plans that were used more than once (see attention_schedule)
+
+
+def pair_halves(full_row_ptr, full_col_idx, part_row_ptr, part_col_idx, seq_len: int, block_m: int, block_n: int):
+    """Chooses, for `stof_block_attn_plan_paired`, which two 64-row halves of the sequence form each 128-row query tile.
+    A tile costs one step per 64-wide key tile that either of its halves lists, so halves with similar lists belong
+    together (rows r and r + 2 of a dilated mask, say).  Greedy matching: the halves with the longest lists choose first
+    and take the free half with which the union is smallest (ties: the neighbour 2t / 2t + 1, then the nearest); then
+    pairs of tiles exchange partners while that shortens the total.
+    Takes the index as host sequences or CPU tensors.  Returns (pairs, steps_default, steps_paired); pairs is a list of
+    ceil(seq_len / 128) (half, half-or--1) tuples, or None when pairing gains less than `_PAIR_MIN_GAIN`.  Pure host code."""
+    import numpy as np
+    frp, fci, prp, pci = (np.asarray(t, dtype=np.int64) for t in (full_row_ptr, full_col_idx, part_row_ptr, part_col_idx))
+    n_half, n_kt, n_rb = (seq_len + 63) // 64, (seq_len + 63) // 64, seq_len // block_m
+    lists = np.zeros((n_half, n_kt), dtype=bool)
+    for rb in range(n_rb):
+        cols = np.concatenate((fci[frp[rb]:frp[rb + 1]], pci[prp[rb]:prp[rb + 1]]))
+        if cols.size == 0:
+            continue
+        h0, h1 = (rb * block_m) // 64, (rb * block_m + block_m - 1) // 64
+        for t in range(block_n // 64 if block_n > 64 else 1):
+            lists[h0:h1 + 1, np.minimum((cols * block_n) // 64 + t, n_kt - 1)] = True
+    if n_half % 2:                                       # an empty dummy half makes the count even; its partner stays alone
+        lists = np.concatenate((lists, np.zeros((1, n_kt), dtype=bool)))
+    n = lists.shape[0]
+    size = lists.sum(axis=1).astype(np.int64)
+    both = lists.astype(np.int64) @ lists.astype(np.int64).T
+    union = size[:, None] + size[None, :] - both
+    steps_default = int(sum(union[2 * t, 2 * t + 1] for t in range(n // 2)))
+    free = np.ones(n, dtype=bool)
+    idx = np.arange(n)
+    pairs = []
+    for a in np.argsort(-size, kind="stable"):
+        if not free[a]:
+            continue
+        free[a] = False
+        # smallest union first; among equals the default neighbour, then the nearest half
+        key = union[a] * (4 * n) + np.where(idx == (a ^ 1), 0, 2 * np.abs(idx - a) + 1)
+        b = int(np.argmin(np.where(free, key, np.iinfo(np.int64).max)))
+        free[b] = False
+        pairs.append([int(a), b])
+    # pairwise exchange: swap partners between two tiles while that shortens the total
+    improved, rounds = True, 0
+    while improved and rounds < 16:
+        improved, rounds = False, rounds + 1
+        for i in range(len(pairs)):
+            for j in range(i + 1, len(pairs)):
+                (a, b), (c, d) = pairs[i], pairs[j]
+                now = union[a, b] + union[c, d]
+                if union[a, c] + union[b, d] < now and union[a, c] + union[b, d] <= union[a, d] + union[b, c]:
+                    pairs[i], pairs[j], improved = [a, c], [b, d], True
+                elif union[a, d] + union[b, c] < now:
+                    pairs[i], pairs[j], improved = [a, d], [b, c], True
+    steps_paired = int(sum(union[a, b] for a, b in pairs))
+    if steps_default == 0 or steps_paired > (1.0 - _PAIR_MIN_GAIN) * steps_default:
+        return None, steps_default, steps_paired
+    out = []
+    for a, b in pairs:
+        a, b = (a, b) if a < b else (b, a)
+        out.append((a, b if b < n_half else -1))
+    out.sort()
+    return out, steps_default, steps_paired
+
+
+def plan_halves(plan, seq_len: int):
+    """View of a plan's half table: int32 (query tiles, 2), the first sequence row of the two 64-row halves of each
+    128-row query tile (-1: no second half)."""
+    nqt, maxt = (seq_len + 127) // 128, (seq_len + 63) // 64
+    a16 = lambda x: (x + 15) & ~15
+    off = 32 + a16(4 * nqt) + a16(8 * nqt) + a16(2 * nqt * maxt) + 64 * nqt * maxt
+    return plan[off:off + 8 * nqt].view(torch.int32).view(nqt, 2)
+
+
+def _build_plan(tensors, pairs, seq_len, block_m, block_n):
+    full_row_ptr, full_col_idx, part_row_ptr, part_col_idx = tensors
     dev = full_row_ptr.device
     L = _lib.lib()
     nbytes = int(L.stof_block_attn_plan_bytes(seq_len, block_m, block_n))
     with torch.cuda.device(dev):
         plan = torch.empty(nbytes, dtype=torch.uint8, device=dev)
-        rc = L.stof_block_attn_plan(_lib.ptr(full_row_ptr), _lib.ptr(full_col_idx), _lib.ptr(part_row_ptr), _lib.ptr(part_col_idx),
-                                    seq_len, int(block_m), int(block_n), _lib.ptr(plan), nbytes, _lib.ptr(_lib.status_word(dev)),
-                                    _lib.current_stream_ptr(dev))
+        common = (seq_len, int(block_m), int(block_n), _lib.ptr(plan), nbytes, _lib.ptr(_lib.status_word(dev)), _lib.current_stream_ptr(dev))
+        if pairs is None:
+            rc = L.stof_block_attn_plan(_lib.ptr(full_row_ptr), _lib.ptr(full_col_idx), _lib.ptr(part_row_ptr), _lib.ptr(part_col_idx), *common)
+        else:
+            pairs_dev = torch.tensor(pairs, dtype=torch.int32).reshape(-1).to(dev)
+            rc = L.stof_block_attn_plan_paired(_lib.ptr(full_row_ptr), _lib.ptr(full_col_idx), _lib.ptr(part_row_ptr),
+                                               _lib.ptr(part_col_idx), _lib.ptr(pairs_dev), *common)
     _lib.check(rc, "stof_block_attn_plan")
-    _PLAN_CACHE[key] = (plan, tensors)
+    return plan
+
+
+def attention_plan(full_row_ptr, full_col_idx, part_row_ptr, part_col_idx, seq_len: int, block_m: int, block_n: int,
+                   pairing: str = "auto"):
+    """Kernel-side plan of a block index (`stof_block_attn_plan`), cached per index: the key holds the four
+    index tensors themselves (their storage cannot be recycled while the entry lives) and their versions.
+    `pairing`: "auto" builds the default plan at the first use of an index and, at its second use, reads the index back
+    once and re-plans with `pair_halves` when that spares tile steps (an index used once is not worth the host read);
+    "eager" does so at once, "off" never."""
+    tensors = (full_row_ptr, full_col_idx, part_row_ptr, part_col_idx)
+    key = tuple((t.data_ptr(), t._version, t.numel()) for t in tensors) + (seq_len, block_m, block_n, str(full_row_ptr.device))
+    hit = _PLAN_CACHE.get(key)
+    if hit is not None:
+        _PLAN_CACHE.move_to_end(key)
+        if hit[2] or pairing == "off":
+            return hit[0]
+    elif pairing != "eager":
+        return _cache_plan(key, _build_plan(tensors, None, seq_len, block_m, block_n), tensors, False)
+    # second use (or "eager"): decide about the pairing, once
+    plan = hit[0] if hit is not None else None
+    pairs = None
+    if seq_len > 128 and block_m <= 64:
+        pairs, _, _ = pair_halves(*(t.cpu() for t in tensors), seq_len, block_m, block_n)
+    if pairs is not None or plan is None:
+        plan = _build_plan(tensors, pairs, seq_len, block_m, block_n)
+    _HOT_PLANS.add(plan.data_ptr())
+    return _cache_plan(key, plan, tensors, True)
+
+
+def _cache_plan(key, plan, tensors, decided):
+    _PLAN_CACHE[key] = (plan, tensors, decided)
     while len(_PLAN_CACHE) > _PLAN_CACHE_MAX:
-        _PLAN_CACHE.popitem(last=False)
+        _HOT_PLANS.discard(_PLAN_CACHE.popitem(last=False)[1][0].data_ptr())
     return plan
 
 
@@ -132,7 +234,7 @@ def block_attention(q, k, v, out, full_row_ptr, full_col_idx, part_row_ptr, part
     dev = q.device
     L = _lib.lib()
     plan = attention_plan(full_row_ptr, full_col_idx, part_row_ptr, part_col_idx, S, int(block_m), int(block_n))
-    schedule, sched_blocks = attention_schedule(plan, S, B, H)
+    schedule, sched_blocks = attention_schedule(plan, S, B, H, eager=plan.data_ptr() in _HOT_PLANS)
     with torch.cuda.device(dev):
         st = _lib.status_word(dev)
         if schedule is None:

@@ -179,3 +179,37 @@ def test_util_helpers_of_the_reference_scripts(tmp_path):
     assert uu.get_best_config(table, 16, 2048) == (64, 64, 4)
     with pytest.raises(ValueError):
         uu.get_best_config(table, 2, 2048)
+
+
+def test_pair_halves_host_logic():
+    """`pair_halves` on block indices given as plain lists: a dilated window pairs halves r and r + 2 and spares tile
+    steps, every half lands in exactly one tile (an odd count leaves one alone), and a plain sliding window, whose
+    neighbours already agree, is left to the default tiling."""
+    import numpy as np
+    from stof_b200.attention import pair_halves
+
+    def index(blocks):
+        ptr, col = [0], []
+        for r in range(blocks.shape[0]):
+            col += np.nonzero(blocks[r])[0].tolist()
+            ptr.append(len(col))
+        return ptr, col
+
+    for nb in (64, 17):
+        i = np.arange(nb)
+        d = i[:, None] - i[None, :]
+        dil = (np.abs(d) <= 4) & (d % 2 == 0)
+        ptr, col = index(dil)
+        pairs, before, after = pair_halves(ptr, col, [0] * (nb + 1), [], nb * 64, 64, 64)
+        assert pairs is not None and after < 0.75 * before
+        flat = [h for p in pairs for h in p if h >= 0]
+        assert sorted(flat) == list(range(nb)) and len(pairs) == (nb + 1) // 2
+        assert sum(1 for p in pairs if p[1] < 0) == nb % 2
+        assert all(p[0] >= 0 and (p[1] < 0 or p[0] < p[1]) for p in pairs)
+        # the same index as partial blocks of 16 x 32
+        ptr16, col16 = index(np.kron(dil, np.ones((4, 2), bool)))
+        pairs16, b16, a16 = pair_halves([0] * (4 * nb + 1), [], ptr16, col16, nb * 64, 16, 32)
+        assert (b16, a16) == (before, after) and pairs16 == pairs
+        slide = np.abs(d) <= 1
+        ptr, col = index(slide)
+        assert pair_halves(ptr, col, [0] * (nb + 1), [], nb * 64, 64, 64)[0] is None

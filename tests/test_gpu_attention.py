@@ -287,3 +287,56 @@ def test_long_sequence_16384_sliding_window_with_partial_blocks():
     torch.cuda.synchronize()
     want = oa.block_attention_from_index(q, k, v, st, 64, 64)
     assert (got.float().cpu() - want).abs().max().item() <= 2e-3
+
+
+@pytest.mark.gpu
+def test_paired_halves_plan_matches_oracle_and_default_plan():
+    """A dilated mask lists different key tiles for neighbouring 64-row halves: at the second use of the index the host
+    pairs halves with like lists (`pair_halves` -> `stof_block_attn_plan_paired`).  Results stay within tolerance of the
+    oracle, every sequence row is written exactly once (odd number of halves: one tile has a single half), and partial
+    blocks keep their tiles (16 x 32 blocks of a token-level dilated mask)."""
+    import stof_b200
+    from stof_b200 import _lib, attention as A
+    dev = torch.device("cuda:0")
+    nb = 17
+    S = nb * 64
+    i = np.arange(nb)
+    d = i[:, None] - i[None, :]
+    blocks = ((np.abs(d) <= 4) & (d % 2 == 0)).astype(np.float32)
+    blocks[:, 0] = 1
+    token = om.generate_dilated_mask(1, S, bandwidth=96, dilation_rate=1).astype(np.float16)
+    for mask, bm, bn in ((om.expand_block_mask(blocks), 64, 64), (token * om.expand_block_mask(blocks), 16, 32)):
+        B, H = 2, 3
+        q, k, v = _qkv(B, H, S, seed=11)
+        qd, kd, vd = q.to(dev), k.to(dev), v.to(dev)
+        idx = _index(mask, bm, bn)
+        first = stof_b200.block_attention(qd, kd, vd, torch.full_like(qd, 7.0), *idx, bm, bn)
+        default_halves = A.plan_halves(A.attention_plan(*idx[:4], S, bm, bn, pairing="off"), S).cpu()    # the cached plan
+        assert torch.equal(default_halves[:, 0], torch.arange(0, S, 128, dtype=torch.int32))
+        second = stof_b200.block_attention(qd, kd, vd, torch.full_like(qd, 7.0), *idx, bm, bn)
+        torch.cuda.synchronize()
+        _lib.check_status(dev, "paired plan")
+        halves = A.plan_halves(A.attention_plan(*idx[:4], S, bm, bn, pairing="off"), S).cpu()
+        assert not torch.equal(halves, default_halves)                                  # the index was re-planned
+        assert sorted(h for h in halves.flatten().tolist() if h >= 0) == list(range(0, S, 64))
+        assert (halves[:, 1] < 0).sum().item() == 1
+        want = oa.masked_attention_fp32(q, k, v, torch.from_numpy(mask.astype(np.float32)))
+        assert _err(first.float().cpu(), want) <= TOL
+        assert _err(second.float().cpu(), want) <= TOL
+        assert _err(first.float().cpu(), second.float().cpu()) <= 1e-3
+    # a pair outside the sequence is reported, not followed
+    L = _lib.lib()
+    idx = _index(om.expand_block_mask(blocks), 64, 64)
+    nbytes = int(L.stof_block_attn_plan_bytes(S, 64, 64))
+    plan = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    pairs = torch.tensor([[2 * t, 2 * t + 1] for t in range((nb + 1) // 2)], dtype=torch.int32)
+    pairs[-1, 1] = -1
+    pairs[3, 1] = nb + 4
+    st = _lib.status_word(dev)
+    rc = L.stof_block_attn_plan_paired(_lib.ptr(idx[0]), _lib.ptr(idx[1]), _lib.ptr(idx[2]), _lib.ptr(idx[3]), _lib.ptr(pairs.to(dev)),
+                                       S, 64, 64, _lib.ptr(plan), nbytes, _lib.ptr(st), _lib.current_stream_ptr(dev))
+    assert rc == 0
+    torch.cuda.synchronize()
+    with pytest.raises(stof_b200.StofError):
+        _lib.check_status(dev, "bad pair")
+    assert A.plan_halves(plan, S)[3].tolist() == [0, -1]
