@@ -301,12 +301,29 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 // Rare paths of the softmax loop are kept out of line (and work on tensor memory, not on the caller's register arrays) so that
 // the loop the warps spend their time in stays a few kilobytes of straight-line code.
 
+// Address of the 16 mask addends (fp16) of this thread's row in column group cg of a partial block (code c >= 2)
+__device__ __forceinline__ const __half* mask_row_ptr(const __half* part_block_mask, int part_base, unsigned c, int bm_shift, int bn,
+                                                      int row_in_block, int col) {
+    return part_block_mask + ((static_cast<size_t>(part_base + c - 2) << bm_shift) + row_in_block) * bn + (col & (bn - 1));
+}
+
 // Applies the block mask to the 32 x 64 scores of one warp in place: column groups a row does not list become -inf, partial
 // groups get their -10000 * (1 - mask) addend.  `cx`, `cy` hold this thread's four group codes.
 __device__ __noinline__ void mask_scores_in_tmem(uint32_t t_s, uint32_t cx, uint32_t cy, const __half* part_block_mask, int part_base, int bm_shift,
                                                  int bn, int row_in_block, int col0) {
     const unsigned code[4] = {cx & 0xFFFFu, cx >> 16, cy & 0xFFFFu, (cy >> 16) & 0x3FFFu};     // the top bits of the last code hold the warp class
-#pragma unroll 1
+    uint4 m[4][2];                                                 // all addends are requested before the first is used
+#pragma unroll
+    for (int cg = 0; cg < 4; ++cg) {
+        m[cg][0] = make_uint4(0u, 0u, 0u, 0u);
+        m[cg][1] = make_uint4(0u, 0u, 0u, 0u);
+        if (code[cg] >= 2u) {
+            const __half* mp = mask_row_ptr(part_block_mask, part_base, code[cg], bm_shift, bn, row_in_block, col0 + cg * 16);
+            m[cg][0] = __ldg(reinterpret_cast<const uint4*>(mp));
+            m[cg][1] = __ldg(reinterpret_cast<const uint4*>(mp + 8));
+        }
+    }
+#pragma unroll
     for (int cg = 0; cg < 4; ++cg) {
         const unsigned c = code[cg];
         if (__all_sync(0xffffffffu, c == 1u)) continue;
@@ -317,12 +334,8 @@ __device__ __noinline__ void mask_scores_in_tmem(uint32_t t_s, uint32_t cx, uint
 #pragma unroll
             for (int i = 0; i < 16; ++i) v[i] = 0xFF800000u;      // -inf
         } else if (c >= 2u) {
-            const int col_in_block = (col0 + cg * 16) & (bn - 1);
-            const __half* mp = part_block_mask + ((static_cast<size_t>(part_base + c - 2) << bm_shift) + row_in_block) * bn + col_in_block;
-            const uint4 u0 = __ldg(reinterpret_cast<const uint4*>(mp));
-            const uint4 u1 = __ldg(reinterpret_cast<const uint4*>(mp + 8));
-            const __half2* h0 = reinterpret_cast<const __half2*>(&u0);
-            const __half2* h1 = reinterpret_cast<const __half2*>(&u1);
+            const __half2* h0 = reinterpret_cast<const __half2*>(&m[cg][0]);
+            const __half2* h1 = reinterpret_cast<const __half2*>(&m[cg][1]);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const float2 a = __half22float2(h0[i]), b = __half22float2(h1[i]);

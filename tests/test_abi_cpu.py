@@ -213,3 +213,22 @@ def test_pair_halves_host_logic():
         slide = np.abs(d) <= 1
         ptr, col = index(slide)
         assert pair_halves(ptr, col, [0] * (nb + 1), [], nb * 64, 64, 64)[0] is None
+
+
+def test_operator_selector_host_logic():
+    """The selector keeps the reference's interface (src/benchmk_attn_unified.py:100-163) and result format; on this
+    kernel it never answers "row-wise" and picks the index granularity from whether partial blocks exist."""
+    from stof_b200 import selector as sel
+    assert len(sel.BLOCK_WISE_CONFIGS) == 36 and {"num_warps": 16, "block_m": 32, "block_n": 128} in sel.BLOCK_WISE_CONFIGS
+    gpu = sel.GPUParams()
+    assert (gpu.gpu_type, gpu.sm_count, gpu.sm_shared) == ("B200", 148, 227 * 1024)
+    assert sel.GPUParams("A100").sm_count == 108 and sel.GPUParams("other").sm_count == 128
+    load_row_ptr = [0, 3, 7, 12]
+    assert sel.select_operator(gpu, load_row_ptr, 8, 4096, 12) == "block-wise warp4m32n32"
+    assert sel.select_operator(gpu, load_row_ptr, 8, 4096, 12, has_partial_blocks=False) == "block-wise warp4m64n64"
+    assert sel.phase1_decision(load_row_ptr, 4096) is True
+    rho, tau = sel.mask_density(load_row_ptr, 4096)
+    assert abs(rho - 12 / 65536) < 1e-12 and abs(tau - 1 / 64) < 1e-12
+    only_wide = [c for c in sel.BLOCK_WISE_CONFIGS if c["block_n"] == 128]
+    assert sel.phase2_selection(only_wide, gpu, 4096, 8, 12)["block_m"] == 32
+    assert sel.phase2_selection([], gpu, 4096, 8, 12) is None

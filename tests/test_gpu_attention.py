@@ -340,3 +340,20 @@ def test_paired_halves_plan_matches_oracle_and_default_plan():
     with pytest.raises(stof_b200.StofError):
         _lib.check_status(dev, "bad pair")
     assert A.plan_halves(plan, S)[3].tolist() == [0, -1]
+
+
+@pytest.mark.gpu
+def test_block_size_selection_and_every_granularity_agree():
+    """`select_block_size`: 64 for a block-aligned mask, 32 for an element-granular one; and the index granularity changes
+    the speed only: every block size gives the same attention within tolerance of the oracle."""
+    import stof_b200
+    S, B, H = 512, 1, 2
+    aligned = om.expand_block_mask(om.block_sliding(S // 64, 1))
+    band = om.generate_sliding_mask(1, S, 40, False, np.float16)
+    assert stof_b200.select_block_size(torch.from_numpy(aligned).cuda()) == 64
+    assert stof_b200.select_block_size(torch.from_numpy(band).cuda()) == 32
+    q, k, v = _qkv(B, H, S, seed=21)
+    want = oa.masked_attention_fp32(q, k, v, torch.from_numpy(band.astype(np.float32)))
+    for blk in (16, 32, 64, 128):
+        got = _run_op(q, k, v, _index(band, blk, blk), blk, blk)
+        assert _err(got, want) <= TOL, blk
