@@ -123,6 +123,8 @@ def attention_plan(full_row_ptr, full_col_idx, part_row_ptr, part_col_idx, seq_l
         return _cache_plan(key, _build_plan(tensors, None, seq_len, block_m, block_n), tensors, False)
     # second use (or "eager"): decide about the pairing, once
     plan = hit[0] if hit is not None else None
+    if plan is not None and torch.cuda.is_current_stream_capturing():
+        return plan                                          # the decision reads the index back: not inside a graph capture
     pairs = None
     if seq_len > 128 and block_m <= 64:
         pairs, _, _ = pair_halves(*(t.cpu() for t in tensors), seq_len, block_m, block_n)
@@ -185,12 +187,12 @@ def attention_schedule(plan, seq_len: int, batch: int, heads: int, eager: bool =
     hit = _SCHED_CACHE.get(key)
     if hit is not None:
         _SCHED_CACHE.move_to_end(key)
-        if hit[0] is None:                                   # second use of this plan and shape: now the table pays off
+        if hit[0] is None and not torch.cuda.is_current_stream_capturing():   # second use of this plan and shape: now the table pays off
             counts = plan[32:32 + 4 * nqt].view(torch.int32).cpu().tolist()
             table, blocks = lpt_schedule(counts, batch * heads, blocks)
             hit = _SCHED_CACHE[key] = (table.to(dev), blocks, plan)
         return hit[0], hit[1]
-    if not eager:
+    if not eager or torch.cuda.is_current_stream_capturing():
         # first use: an index that is used once (a caller-supplied row mask, a test) is not worth a host read and a few
         # milliseconds of host work; remember it and run the default deal
         _SCHED_CACHE[key] = (None, 0, plan)
