@@ -56,18 +56,19 @@ def pair_halves(full_row_ptr, full_col_idx, part_row_ptr, part_col_idx, seq_len:
         free[b] = False
         pairs.append([int(a), b])
     # pairwise exchange: swap partners between two tiles while that shortens the total
+    union = union.tolist()                               # plain lists: the loop below is scalar work
     improved, rounds = True, 0
     while improved and rounds < 16:
         improved, rounds = False, rounds + 1
         for i in range(len(pairs)):
             for j in range(i + 1, len(pairs)):
                 (a, b), (c, d) = pairs[i], pairs[j]
-                now = union[a, b] + union[c, d]
-                if union[a, c] + union[b, d] < now and union[a, c] + union[b, d] <= union[a, d] + union[b, c]:
+                now, swap1, swap2 = union[a][b] + union[c][d], union[a][c] + union[b][d], union[a][d] + union[b][c]
+                if swap1 < now and swap1 <= swap2:
                     pairs[i], pairs[j], improved = [a, c], [b, d], True
-                elif union[a, d] + union[b, c] < now:
+                elif swap2 < now:
                     pairs[i], pairs[j], improved = [a, d], [b, c], True
-    steps_paired = int(sum(union[a, b] for a, b in pairs))
+    steps_paired = int(sum(union[a][b] for a, b in pairs))
     if steps_default == 0 or steps_paired > (1.0 - _PAIR_MIN_GAIN) * steps_default:
         return None, steps_default, steps_paired
     out = []
