@@ -184,6 +184,18 @@ def test_rowwise_operators_match_their_oracles():
     assert _err(got.float().cpu(), oa.rowwise_mask(q, k, v, False, rm)) <= TOL
     got = rowwise_attn_mask_op(qd, kd, vd, True, (rm * 3).cuda())          # any positive value admits a key
     assert _err(got.float().cpu(), oa.rowwise_mask(q, k, v, True, rm)) <= TOL
+    # the index of a caller's mask is cached under the tensor's identity and version: the same tensor again gives the same
+    # result without a rebuild, an in-place change of the mask is seen
+    from stof_b200 import rowwise as rw
+    rmd = rm.cuda()
+    first = rowwise_attn_mask_op(qd, kd, vd, False, rmd)
+    entries = len(rw._INDEX_CACHE)
+    assert torch.equal(rowwise_attn_mask_op(qd, kd, vd, False, rmd), first) and len(rw._INDEX_CACHE) == entries
+    rmd[:, S // 2:] = 0
+    rmd += torch.eye(S, dtype=torch.float16, device="cuda")
+    rmd.clamp_(max=1)
+    got = rowwise_attn_mask_op(qd, kd, vd, False, rmd)
+    assert _err(got.float().cpu(), oa.rowwise_mask(q, k, v, False, rmd.cpu())) <= TOL
     res = torch.zeros(B, S, H * 64, dtype=torch.float16, device="cuda")
     ext_full.forward(qd, kd, vd, True, res)                                 # extension-module form: result pre-allocated by the caller
     assert _err(res.float().cpu(), oa.rowwise_full(q, k, v, True)) <= TOL
