@@ -43,6 +43,29 @@ def test_gemm_bias_gelu(mode):
     assert _err(got, want) <= 2e-3 * max(1.0, want.abs().max().item())
 
 
+@pytest.mark.parametrize("m,n,k", [(4096, 2560, 136), (4136, 2568, 72), (37 * 256 + 129, 1024, 64)])
+def test_large_gemm_on_block_pairs_every_epilogue(m, n, k):
+    """Shapes with at least two 256 x 256 tiles per pair of SMs run on the two-block (cta_group::2) kernel: every epilogue,
+    ragged edges in both directions (a last tile whose second block has no rows at all, or only one), a K that is not a
+    multiple of the 64-wide stage, and a GELU check against erf on values across the polynomial's whole range."""
+    import stof_b200
+    a, w, b, r = _rand((m, k), 11), _rand((k, n), 12, 0.1), _rand((n,), 13), _rand((m, n), 14)
+    ad, wd, bd, rd = a.cuda(), w.cuda(), b.cuda(), r.cuda()
+    base = of.gemm_bias(a, w, b)
+    tol = 2e-3 * max(1.0, base.abs().max().item())
+    assert _err(stof_b200.gemm_bias(ad, wd, bd), base) <= tol
+    assert _err(stof_b200.gemm_bias_residual(ad, wd, bd, rd), base + r.float()) <= 2 * tol
+    assert _err(stof_b200.gemm_bias_relu(ad, wd, bd), torch.relu(base)) <= tol
+    for mode in ("erf", "tanh"):
+        assert _err(stof_b200.gemm_bias_gelu(ad, wd, bd, mode), of.gemm_bias_gelu(a, w, b, mode)) <= tol
+    wide = _rand((m, k), 15, 4.0)                                          # pre-activations well beyond +-4.5
+    want = of.gemm_bias_gelu(wide, w, b, "erf")
+    assert _err(stof_b200.gemm_bias_gelu(wide.cuda(), wd, bd, "erf"), want) <= 2e-3 * max(1.0, want.abs().max().item())
+    torch.cuda.synchronize()
+    from stof_b200 import _lib
+    _lib.check_status(torch.device("cuda:0"), "pair gemm")
+
+
 def test_gemm_bias_residual_and_3d_inputs():
     import stof_b200
     a, w, b, r = _rand((4, 96, 128), 7), _rand((128, 256), 8, 0.1), _rand((256,), 9), _rand((4, 96, 256), 10)
