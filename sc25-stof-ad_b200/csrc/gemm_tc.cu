@@ -341,7 +341,9 @@ extern "C" int stof_gemm_bias_act(const void* a, long long lda, const void* w, l
         // pairs of blocks on 256 x 256 tiles once every pair of SMs gets at least two of them; small problems keep 128 x 256 tiles
         const long long tiles256 = static_cast<long long>((m + 255) / 256) * ((n + 255) / 256);
         const int mode = pair_mode();
-        if (mode == 1 || (mode < 0 && tiles256 >= 2LL * (sm_count() / 2)))
+        // (the residual epilogue outlasts a main loop of K <= 1024 in both kernels; there the one-block kernel's shorter tiles win)
+        const bool short_residual = epilogue == STOF_EPI_BIAS_RESIDUAL && k <= 1024;
+        if (mode == 1 || (mode < 0 && !short_residual && tiles256 >= 2LL * (sm_count() / 2)))
             return gemm_pair_dispatch(ma, mw, mc, bp, rp, ldr, m, n, k, epilogue, status_dev, stream);
     }
     switch (epilogue) {
