@@ -6,11 +6,13 @@
 // the pair's A halves with both W halves.  Per SM and per flop that is half the W bytes through shared memory, TMA and L2 of
 // the one-block kernel, which is what the power-capped rate of long GEMMs depends on.
 //   warp 8      TMA producer (both blocks): own A box and two 64 x 64 W boxes per stage, 6 stages of 32 KB; every copy
-//               reports to the LEADER's full barrier.  The leader forwards "stage free" to its peer with a remote arrive
-//   warp 9      leader only: MMA issuer, two 256-column accumulators; tcgen05.commit on the leader's own barriers
-//   warps 0-7   epilogue (both blocks), same as the one-block kernel; the leader forwards "accumulator full" to its peer,
-//               the peer reports "accumulator drained" to the leader with remote arrives
-// No copy or commit carries a cluster multicast: the cross-block signals are plain mbarrier arrives on mapped addresses.
+//               reports its bytes to the LEADER's full barrier (the leader arms it for both blocks' bytes)
+//   warp 9      leader only: MMA issuer, two 256-column accumulators; after the MMAs of a stage (a tile) it commits twice,
+//               once on its own "stage free" ("accumulator full") barrier and once on its peer's, by mapped address
+//   warps 0-7   epilogue (both blocks), same as the one-block kernel; the peer's warps report "accumulator drained" to the
+//               leader's barrier with remote mbarrier arrives
+// Every copy and every commit names exactly one block's barrier.  Both blocks meet at a cluster barrier before they leave, so
+// that neither frees shared or tensor memory its peer may still signal, read or write.
 #include "stof_host.h"
 #include "stof_ptx.cuh"
 
