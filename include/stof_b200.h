@@ -169,6 +169,11 @@ int stof_block_attn_scheduled(const void* q, const void* k, const void* v, void*
  * epilogue: STOF_EPI_BIAS, _GELU_ERF, _GELU_TANH, _RESIDUAL (adds residual[M,N], row stride ldr), _RELU
  * (max(x, 0): the FFN activation of the T5 loops, src/benchmk_end2end.py:203,313).
  * bias may be NULL.
+ * Two kernels serve the call: shapes with at least two 256 x 256 tiles per pair of multiprocessors run on
+ * pairs of thread blocks (tcgen05 cta_group::2, clusters of two), smaller ones and residual epilogues with
+ * K <= 1024 on single blocks with 128 x 256 tiles; the results agree within fp16 rounding.  The
+ * environment variable STOF_B200_GEMM_PAIR = 0 / 1, read once per process, forces one of the two
+ * (a testing aid).  GELU_ERF evaluates x * Phi(x) with a polynomial (|error| < 1.1e-4).
  * ------------------------------------------------------------------------------------------ */
 #define STOF_EPI_BIAS 0
 #define STOF_EPI_BIAS_GELU_ERF 1
