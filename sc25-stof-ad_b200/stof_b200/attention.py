@@ -275,15 +275,27 @@ class HostAttentionPipeline:
     the output overwrites the q slot, as the reference operator does) is allocated once and reused by later calls
     of the same shape."""
 
-    def __init__(self, device, chunk_batch: int = 2, slots: int = 3):
+    def __init__(self, device, chunk_batch: int = 2, slots: int = 3, taper: int = 2):
         self.device = torch.device(device)
         self.chunk = int(chunk_batch)
         self.slots = int(slots)
+        self.taper = int(taper)
         self._shape = None
         self._stage = None
         self._s_in = torch.cuda.Stream(self.device)
         self._s_run = torch.cuda.Stream(self.device)
         self._s_out = torch.cuda.Stream(self.device)
+
+    def chunk_sizes(self, batch: int):
+        """Batch elements per chunk: full chunks, the last one halved `taper` times (4 -> 2, 1, 1): what follows the last
+        host-to-device copy - its kernel and the copy of its result back - is then a small chunk's worth."""
+        sizes = [min(self.chunk, batch - b0) for b0 in range(0, batch, self.chunk)]
+        for _ in range(self.taper):
+            if not sizes or sizes[-1] < 2:
+                break
+            x = sizes.pop()
+            sizes += [x - x // 2, x // 2]
+        return sizes
 
     def _staging(self, heads, seq_len, head_dim):
         shape = (self.chunk, heads, seq_len, head_dim)
@@ -308,8 +320,9 @@ class HostAttentionPipeline:
             st.wait_event(start)                       # everything enqueued before the call comes first
         slot_free = [None] * self.slots
         last = None
-        for c, b0 in enumerate(range(0, B, self.chunk)):
-            nb = min(self.chunk, B - b0)
+        sizes = self.chunk_sizes(B)
+        starts = [sum(sizes[:i]) for i in range(len(sizes))]
+        for c, (b0, nb) in enumerate(zip(starts, sizes)):
             qd, kd, vd = (t[:nb] for t in stage[c % self.slots])
             with torch.cuda.stream(self._s_in):
                 if slot_free[c % self.slots] is not None:
