@@ -267,6 +267,18 @@ def block_attn_mask(q, k, v, full_row_ptr, full_col_idx, part_row_ptr, part_col_
                            part_block_mask.contiguous(), load_row_ptr, load_col_idx, BLOCK_M, BLOCK_N, num_warps)
 
 
+def tapered_chunks(batch: int, chunk: int, taper: int):
+    """Batch elements per chunk of the host pipeline: full chunks, the last one halved `taper` times (4 -> 2, 1, 1): what
+    follows the last host-to-device copy - its kernel and the copy of its result back - is then a small chunk's worth."""
+    sizes = [min(chunk, batch - b0) for b0 in range(0, batch, chunk)]
+    for _ in range(taper):
+        if not sizes or sizes[-1] < 2:
+            break
+        x = sizes.pop()
+        sizes += [x - x // 2, x // 2]
+    return sizes
+
+
 class HostAttentionPipeline:
     """Block-masked attention for q, k, v that live in (pinned) HOST memory: the batch is cut into chunks that go
     through three CUDA streams - host-to-device copies of chunk c+1, the attention kernel on chunk c and the
@@ -287,15 +299,7 @@ class HostAttentionPipeline:
         self._s_out = torch.cuda.Stream(self.device)
 
     def chunk_sizes(self, batch: int):
-        """Batch elements per chunk: full chunks, the last one halved `taper` times (4 -> 2, 1, 1): what follows the last
-        host-to-device copy - its kernel and the copy of its result back - is then a small chunk's worth."""
-        sizes = [min(self.chunk, batch - b0) for b0 in range(0, batch, self.chunk)]
-        for _ in range(self.taper):
-            if not sizes or sizes[-1] < 2:
-                break
-            x = sizes.pop()
-            sizes += [x - x // 2, x // 2]
-        return sizes
+        return tapered_chunks(batch, self.chunk, self.taper)
 
     def _staging(self, heads, seq_len, head_dim):
         shape = (self.chunk, heads, seq_len, head_dim)

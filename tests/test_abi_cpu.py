@@ -232,3 +232,18 @@ def test_operator_selector_host_logic():
     only_wide = [c for c in sel.BLOCK_WISE_CONFIGS if c["block_n"] == 128]
     assert sel.phase2_selection(only_wide, gpu, 4096, 8, 12)["block_m"] == 32
     assert sel.phase2_selection([], gpu, 4096, 8, 12) is None
+
+
+def test_host_pipeline_chunking():
+    """Chunk sizes of the host-buffer pipeline: they cover the batch in order, none exceeds the staging size, and the tail is
+    tapered so that little work follows the last inbound copy."""
+    from stof_b200.attention import tapered_chunks
+    assert tapered_chunks(16, 4, 0) == [4, 4, 4, 4]
+    assert tapered_chunks(16, 4, 2) == [4, 4, 4, 2, 1, 1]
+    assert tapered_chunks(7, 3, 1) == [3, 3, 1]
+    assert tapered_chunks(1, 4, 2) == [1]
+    assert tapered_chunks(0, 4, 2) == []
+    for batch in range(1, 20):
+        for chunk in (1, 2, 5):
+            sizes = tapered_chunks(batch, chunk, 2)
+            assert sum(sizes) == batch and max(sizes) <= chunk and min(sizes) >= 1
