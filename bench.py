@@ -3,15 +3,20 @@
 
     python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload attention|encoder]
 
-N > 1 is launched with torchrun, one rank per GPU; ranks own independent shards (weak scaling for
-attention: every rank runs the full configuration on its own seeded batch; the encoder shards the
-configuration's batch).  No collective runs inside the timed region.  Rank 0 prints ONE JSON line.
+N > 1 is launched with torchrun, one rank per GPU; ranks own independent shards.  The headline attention
+number weak-scales (every rank runs the full configuration on its own seeded batch); the same line carries
+the strong-scaled forms: configurations 2 and 3 sharded over batch x heads ("attention_sharded", every rank a
+slice of the SAME seeded tensors, outputs gathered over NCCL after the timing and compared on rank 0) and the
+encoder with its batch sharded.  No collective runs inside a timed region.  Rank 0 prints ONE JSON line.
 
 A step = one pass of the hot path over one batch of synthetic input: one attention launch over all
 (batch, head) problems of the configuration with the block index already built (the reference
 benchmark builds the index outside its timed loop too, src/benchmk_attn_unified.py:315-346).
 Between timed steps a 256 MiB buffer is written to flush L2; each step is timed with its own CUDA
-event pair on the launching stream, and the sum over the K steps is reduced with max over ranks.
+event pair on the launching stream.  Blocks of exactly K such steps are repeated until a quarter of a
+second of timed steps has run (so that the clock samples fall inside the timed region); the figure is the
+median block, reduced with max over ranks, and the fastest block is reported beside it.  The output of
+the last timed step is then compared with the CPU oracle on four (batch, head) pairs.
 """
 from __future__ import annotations
 
@@ -97,6 +102,59 @@ def physical_gpu_index(local_rank: int) -> int:
     return local_rank
 
 
+def attention_config_dict(cfg, n_load_blocks, flops, parallelism):
+    """The `config` object of an attention line; both arms print exactly these keys for the same workload."""
+    return {"workload": cfg.name, "batch_per_gpu": cfg.batch, "heads": cfg.heads, "seq_len": cfg.seq_len, "head_dim": cfg.head_dim,
+            "mask": f"{cfg.mask} block {cfg.block}", "load_blocks": n_load_blocks, "flops_per_step_per_gpu": flops,
+            "l2": "256 MiB flush write between timed steps", "parallelism": parallelism}
+
+
+# DRAM read + write bytes of one block_attn_kernel launch, from the ncu capture summarised under profiles/ (file named per
+# entry), with the batch that capture ran at: every (batch, head) pair is an independent set of work items, so the traffic
+# of a launch grows in proportion to the batch.
+NCU_TRAFFIC = {
+    "mha_bigbird_b16_h12_s2048": {"bytes": 85.22e6, "batch": 8, "profile": "profiles/block_attn_kernel_cfg2_batch8.md"},
+}
+
+
+def timed_step_blocks(step, flush, steps, dev, min_ms=250.0, max_blocks=400, est_ms=None):
+    """Runs blocks of exactly `steps` steps, each step after an L2 flush and inside its own CUDA event pair on the current
+    stream, until `min_ms` of timed device time has been spent; returns the per-block sums in ms.  The number of blocks is
+    fixed beforehand from `est_ms` (an estimate of one step) so that every rank runs the same count."""
+    n_blocks = 1 if not est_ms else max(1, min(max_blocks, int(min_ms / (est_ms * steps)) + 1))
+    sums = []
+    for _ in range(n_blocks):
+        starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        for i in range(steps):
+            flush.zero_()
+            starts[i].record()
+            step()
+            ends[i].record()
+        torch.cuda.synchronize(dev)
+        sums.append(sum(a.elapsed_time(b) for a, b in zip(starts, ends)))
+    return sums
+
+
+def median(xs):
+    xs = sorted(xs)
+    return xs[len(xs) // 2] if len(xs) % 2 else 0.5 * (xs[len(xs) // 2 - 1] + xs[len(xs) // 2])
+
+
+def attention_parity(out, q, k, v, mask, pairs):
+    """Largest |difference| between the kernel output `out` (device) and the oracle's fp32 dense masked attention on the given
+    (batch, head) pairs; q, k, v (B,H,S,D) and mask (1,S,S) are the CPU tensors the device inputs were made from."""
+    from oracle import attention as oa
+    worst = 0.0
+    for b, h in pairs:
+        want = oa.masked_attention_fp32(q[b:b + 1, h:h + 1], k[b:b + 1, h:h + 1], v[b:b + 1, h:h + 1], mask.float())
+        worst = max(worst, (out[b:b + 1, h:h + 1].float().cpu() - want).abs().max().item())
+    return worst
+
+
+PARITY_TOL = 2e-3          # max-abs against the fp32 oracle, fp16 inputs with fp32 accumulation
+
+
 # --------------------------------------------------------------------------------------------
 # CPU baseline: the reference's PyTorch-native path (oracle port) on the host cores
 # --------------------------------------------------------------------------------------------
@@ -151,8 +209,7 @@ def run_reference(args):
     line = {"impl": "reference", "metric": "masked-MHA effective TFLOP/s", "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs * 1e3, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": cfg.name, "batch": cfg.batch, "heads": cfg.heads, "seq_len": cfg.seq_len, "head_dim": 64,
-                       "mask": "bigbird block 64: 3 sliding + 2 global + 3 random per row (seed 1)", "load_blocks": nb},
+            "config": attention_config_dict(cfg, nb, wl.attention_flops(nb, cfg.batch, cfg.heads), f"independent batch shards x{args.gpus}"),
             "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0, "wall_s": wall}
@@ -236,32 +293,25 @@ def run_attention(args, rank, world, local):
         step()
     torch.cuda.synchronize(dev)
     _lib.check_status(dev, "warm-up")
+    ev0.record()
+    step()
+    ev1.record()
+    torch.cuda.synchronize(dev)
+    est_ms = sd.max_over_ranks(ev0.elapsed_time(ev1), dev)
 
-    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     if world > 1:
         torch.distributed.barrier()
     torch.cuda.synchronize(dev)
     with ClockSampler(physical_gpu_index(local)) as clocks:
         t_wall = time.perf_counter()
-        for i in range(args.steps):
-            flush.zero_()
-            starts[i].record()
-            step()
-            ends[i].record()
-        torch.cuda.synchronize(dev)
+        block_ms = timed_step_blocks(step, flush, args.steps, dev, min_ms=0.0 if args.kernel_only else 250.0, est_ms=est_ms)
         wall = time.perf_counter() - t_wall
-        # keep the GPU under the same load a little longer so that the clock sampler sees it
-        t_end = time.perf_counter() + (0.0 if args.kernel_only else 0.25)
-        while time.perf_counter() < t_end:
-            step()
-        torch.cuda.synchronize(dev)
     if world > 1:
         torch.distributed.barrier()
     _lib.check_status(dev, "timed region")
-    dev_ms = sum(s.elapsed_time(e) for s, e in zip(starts, ends))
-    dev_ms_max = sd.max_over_ranks(dev_ms, dev)
-    ms_per_step = dev_ms_max / args.steps
+    dev_ms = median(block_ms)                                  # K steps of this rank
+    ms_per_step = sd.max_over_ranks(dev_ms, dev) / args.steps
+    ms_per_step_min = sd.max_over_ranks(min(block_ms), dev) / args.steps
     total_flops = flops * world
     value = total_flops / (ms_per_step * 1e-3) / 1e12
 
@@ -271,6 +321,11 @@ def run_attention(args, rank, world, local):
             print(json.dumps({"metric": "masked-MHA effective TFLOP/s", "value": value, "unit": "TFLOP/s", "ms_per_step": ms_per_step,
                               "config": {"workload": cfg.name, "load_blocks": n_load}, "note": "kernel-only run (profiling aid)"}))
         return 0
+    # parity of what was timed: the output of the last timed step against the fp32 oracle on four (batch, head) pairs
+    pairs = sorted({(0, 0), (cfg.batch // 2, cfg.heads // 3), (cfg.batch - 1, cfg.heads - 1), (min(1, cfg.batch - 1), 5 % cfg.heads)})
+    parity = attention_parity(out, q_h, k_h, v_h, wl.config_mask(cfg), pairs) if rank == 0 else 0.0
+    out_full = out.clone() if (world > 1 and rank == 0 and args.config == "cfg2" and not args.batch) else None
+
     # end to end with host buffers through the host-buffer form of the operator: H2D of q, k, v, the kernel (in place on q, as
     # the reference operator does) and D2H of the result, batch chunks pipelined over three streams
     e2e_steps = args.steps
@@ -292,32 +347,40 @@ def run_attention(args, rank, world, local):
     e2e_value = total_flops / (e2e_ms * 1e-3) / 1e12
     h2d = 3 * q_h.numel() * 2
     d2h = out_h.numel() * 2
+    e2e_parity = attention_parity(out_h, q_h, k_h, v_h, wl.config_mask(cfg), pairs[:2]) if rank == 0 else 0.0
 
-    encoder = None
     alg_bytes = 4 * q.numel() * 2
+    q = k = v = out = None
+    sharded = None
+    if world > 1:
+        # strong scaling: configurations 2 and 3 split over batch x heads, every rank a slice of the same seeded tensors
+        sharded = [attention_sharded(args, rank, world, local, wl.ATTENTION_CONFIGS[c], flush, out_full if c == "cfg2" else None)
+                   for c in ("cfg2", "cfg3")]
+    encoder = None
     if not args.no_encoder:
-        q = k = v = out = flush = None
+        out_full = flush = None
         torch.cuda.empty_cache()
-        encoder = encoder_measure(args, rank, world, local, steps=max(2, min(args.steps, 3)), warmup=3)
+        encoder = encoder_measure(args, rank, world, local, steps=max(args.steps, 20) if world > 1 else max(8, min(args.steps, 20)), warmup=3)
     if rank != 0:
         return 0
-    # parity spot check of the timed output against the oracle is the job of the tests; here only sanity
-    finite = bool(torch.isfinite(out_h.float()).all())
     cpu_val, cpu_s, cpu_desc = cpu_attention_sample(cfg, n_load, 10.0)
     mask_bytes = mask.numel() * 2
     comp_best = min(comp_ms)
     achieved = flops / (dev_ms / args.steps * 1e-3) / 1e12       # this rank's kernel
-    # DRAM read+write bytes of one launch from an ncu capture at batch 8 of the same mask (86.2 MB), scaled by batch
-    traffic = 86.230e6 * cfg.batch / 8 if cfg.mask == "bigbird" and cfg.seq_len == 2048 and cfg.heads == 12 else None
+    tr = NCU_TRAFFIC.get(cfg.name.split("_batch")[0])
+    traffic = tr["bytes"] * cfg.batch / tr["batch"] if tr else None
     line = {
         "metric": "masked-MHA effective TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f16", "data": "synthetic",
-        "config": {"workload": cfg.name, "batch_per_gpu": cfg.batch, "heads": cfg.heads, "seq_len": cfg.seq_len, "head_dim": cfg.head_dim,
-                   "mask": f"{cfg.mask} block {cfg.block}", "load_blocks": n_load, "flops_per_step_per_gpu": flops,
-                   "l2": "256 MiB flush write between timed steps", "parallelism": f"independent batch shards x{world}"},
+        "config": attention_config_dict(cfg, n_load, flops, f"independent batch shards x{world}"),
+        "timed_blocks": {"blocks_of_k_steps": len(block_ms), "ms_per_step_median": ms_per_step, "ms_per_step_min": ms_per_step_min,
+                         "timed_device_ms": sum(block_ms)},
+        "parity": {"max_abs_vs_fp32_oracle": parity, "tolerance": PARITY_TOL, "batch_head_pairs": [list(x) for x in pairs],
+                   "of": "output of the last timed step", "e2e_max_abs": e2e_parity},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
-                     "traffic": traffic, "traffic_unit": "bytes per launch (ncu dram read+write, batch-8 capture scaled)",
+                     "traffic": traffic, "traffic_unit": "bytes per launch (ncu dram read+write of a smaller batch, scaled by batch)",
+                     "traffic_source": tr["profile"] if tr else None,
                      "algorithmic_bytes": alg_bytes, "peak_source": peaks["source"] + " bf16 burst",
                      "frac_of_sustained": achieved / peaks["tflops_sustained"], "kernel": "block_attn_kernel"},
         "cpu_baseline": {"value": cpu_val, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port", "sample": cpu_desc,
@@ -330,12 +393,118 @@ def run_attention(args, rank, world, local):
                        "note": "classify + fill + host read of the three totals, S=%d" % cfg.seq_len,
                        "kernels_back_to_back_us": comp_eager_us, "kernels_graph_replay_us": comp_graph_us,
                        "kernels_gbs": mask_bytes / (comp_graph_us * 1e-6) / 1e9},
-        "wall_s_timed_region": wall, "output_finite": finite,
+        "wall_s_timed_region": wall,
     }
+    if sharded is not None:
+        line["attention_sharded"] = sharded
     if encoder is not None:
         line["encoder"] = encoder
+    ok = parity <= PARITY_TOL and e2e_parity <= PARITY_TOL and all(r is None or r.get("ok", True) for r in (sharded or [])) and \
+        (encoder is None or encoder.get("parity_first_layer", {}).get("ok", True))
+    if not ok:
+        line["error"] = "parity check failed"
     print(json.dumps(line))
-    return 0
+    return 0 if ok else 1
+
+
+def attention_sharded(args, rank, world, local, cfg, flush, full_out_rank0):
+    """One attention configuration split over batch x heads (`dist.attention_shard`): every rank runs its slice of the SAME
+    seeded q, k, v; aggregate effective TFLOP/s = FLOPs of the whole configuration / the slowest rank's time.  After the timing the
+    slices are gathered over NCCL (the one collective of this path, verification only) and rank 0 compares the whole tensor
+    with the fp32 oracle on (batch, head) pairs from different ranks' slices - and bit for bit with its own single-GPU result of
+    the same configuration when it has one (`full_out_rank0`)."""
+    import stof_b200
+    from stof_b200 import _lib, dist as sd, workloads as wl
+    dev = torch.device("cuda", local)
+    (b0, b1), (h0, h1) = sd.attention_shard(cfg.batch, cfg.heads, rank, world)
+    q_h, k_h, v_h = wl.attention_inputs(cfg)
+    q, k, v = (t[b0:b1, h0:h1].contiguous().to(dev) for t in (q_h, k_h, v_h))
+    out = torch.empty_like(q)
+    idx = stof_b200.get_sparse_storage(wl.config_mask(cfg).to(dev), cfg.block, cfg.block)[1:]
+    n_load = int(idx[5][-1].item())
+
+    def step():
+        stof_b200.block_attention(q, k, v, out, *idx, cfg.block, cfg.block)
+
+    for _ in range(max(args.warmup, 3)):
+        flush.zero_()
+        step()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    step()
+    ev1.record()
+    torch.cuda.synchronize(dev)
+    est_ms = sd.max_over_ranks(ev0.elapsed_time(ev1), dev)
+    torch.distributed.barrier()
+    block_ms = timed_step_blocks(step, flush, args.steps, dev, min_ms=100.0, est_ms=est_ms)
+    torch.distributed.barrier()
+    _lib.check_status(dev, "sharded attention")
+    ms = sd.max_over_ranks(median(block_ms), dev) / args.steps
+    split_dim = 1 if (h1 - h0) < cfg.heads else 0
+    whole = sd.gather_shards(out, cfg.batch if split_dim == 0 else cfg.heads, dim=split_dim)
+    if rank != 0:
+        return None
+    flops = wl.attention_flops(n_load, cfg.batch, cfg.heads, cfg.block, cfg.block, cfg.head_dim)
+    pairs = sorted({(0, 0), (cfg.batch - 1, cfg.heads - 1), (cfg.batch // 2, cfg.heads // 2), (cfg.batch // 2 + cfg.batch // 4, 1 % cfg.heads)})
+    parity = attention_parity(whole, q_h, k_h, v_h, wl.config_mask(cfg), pairs)
+    same = bool(torch.equal(whole, full_out_rank0)) if full_out_rank0 is not None else None
+    return {"workload": cfg.name, "scaling": "strong", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms,
+            "shard": f"batch {b1 - b0} x heads {h1 - h0} per GPU", "load_blocks": n_load, "timed_blocks": len(block_ms),
+            "gathered_over_nccl": {"max_abs_vs_fp32_oracle": parity, "batch_head_pairs": [list(x) for x in pairs],
+                                   "bit_identical_to_single_gpu_result": same},
+            "ok": parity <= PARITY_TOL and same is not False}
+
+
+def encoder_parity(enc_layers, cfg, x_first_seq, dev, depth_report: bool):
+    """Parity of the encoder on sequence 0 of the batch against the fp32 oracle (dense masked attention on the CPU):
+    the first layer alone, and - when `depth_report` - the whole stack, with the error of the reference's own fp16 path
+    (PyTorch eager on the same GPU: fp16 matmuls, softmax, layer_norm, erf GELU, src/benchmk_end2end.py:31-88) beside it, so that
+    the growth of rounding error through the layers is on record for both."""
+    import stof_b200
+    from oracle import fused as of
+    from stof_b200 import workloads as wl
+    mask_cpu = wl.config_mask(cfg)
+    params = wl.encoder_weights(cfg)
+    one = stof_b200.BertEncoder(enc_layers[:1], cfg.heads, cfg.eps, "erf", cfg.block, cfg.block)
+    one.set_mask(mask_cpu.to(dev))
+    got1 = one(x_first_seq.to(dev)).float().cpu()
+    want1 = of.bert_layer(x_first_seq, params[0], mask_cpu.float(), cfg.heads, eps=cfg.eps)
+    err1 = (got1 - want1).abs().max().item()
+    scale1 = max(1.0, want1.abs().max().item())
+    rec = {"max_abs_vs_fp32_oracle": err1, "tolerance": PARITY_TOL * scale1, "output_max_abs": want1.abs().max().item(),
+           "of": "layer 1 on sequence 0 (tolerance = 2e-3 x the output magnitude: one fp16 step grows with it)",
+           "ok": err1 <= PARITY_TOL * scale1}
+    if depth_report:
+        full = stof_b200.BertEncoder(enc_layers, cfg.heads, cfg.eps, "erf", cfg.block, cfg.block)
+        full.set_mask(mask_cpu.to(dev))
+        got = full(x_first_seq.to(dev)).float().cpu()
+        want = of.encoder_forward(x_first_seq, params, mask_cpu.float(), cfg.heads, cfg.eps)
+        eager = torch_eager_fp16_encoder(x_first_seq.to(dev), enc_layers, mask_cpu.to(dev), cfg.heads, cfg.eps).float().cpu()
+        rec["all_layers"] = {"layers": cfg.layers, "max_abs_vs_fp32_oracle": (got - want).abs().max().item(),
+                             "mean_abs_vs_fp32_oracle": (got - want).abs().mean().item(),
+                             "torch_eager_fp16_max_abs_vs_fp32_oracle": (eager - want).abs().max().item(),
+                             "torch_eager_fp16_mean_abs_vs_fp32_oracle": (eager - want).abs().mean().item(),
+                             "output_max_abs": want.abs().max().item(),
+                             "note": "last layer's output of sequence 0, as the reference's end-to-end check compares it"}
+    return rec
+
+
+def torch_eager_fp16_encoder(x, layers, mask, heads, eps):
+    """The reference's PyTorch-native fp16 forward on the GPU (library kernels; a comparison figure for the parity report only)."""
+    import torch.nn.functional as F
+    B, S, hid = x.shape
+    d = hid // heads
+    add_mask = (1.0 - mask[:, None].half()) * -10000.0
+    h = x
+    for w in layers:
+        qkv = torch.matmul(h, w.Wqkv) + w.bqkv
+        q, k, v = (t.view(B, S, heads, d).permute(0, 2, 1, 3) for t in qkv.chunk(3, dim=-1))
+        scores = torch.matmul(q, k.transpose(-2, -1)) / (d ** 0.5) + add_mask
+        ctx = torch.matmul(F.softmax(scores, dim=-1), v).permute(0, 2, 1, 3).contiguous().view(B, S, hid)
+        h = F.layer_norm(torch.matmul(ctx, w.Wo) + w.bo + h, (hid,), w.g1, w.b1, eps)
+        f = F.gelu(torch.matmul(h, w.W1) + w.bi1)
+        h = F.layer_norm(torch.matmul(f, w.W2) + w.bi2 + h, (hid,), w.g2, w.b2, eps)
+    return h
 
 
 def encoder_measure(args, rank, world, local, steps, warmup):
@@ -359,23 +528,33 @@ def encoder_measure(args, rank, world, local, steps, warmup):
     if world > 1:
         torch.distributed.barrier()
     torch.cuda.synchronize(dev)
-    e0.record()
-    for _ in range(steps):
-        enc(x)
-    e1.record()
-    torch.cuda.synchronize(dev)
+    with ClockSampler(physical_gpu_index(local)) as clocks:
+        e0.record()
+        for _ in range(steps):
+            enc(x)
+        e1.record()
+        torch.cuda.synchronize(dev)
     if world > 1:
         torch.distributed.barrier()
     _lib.check_status(dev, "encoder timed region")
-    ms = sd.max_over_ranks(e0.elapsed_time(e1), dev) / steps
+    my_ms = e0.elapsed_time(e1) / steps
+    ms = sd.max_over_ranks(my_ms, dev)
+    # per-rank time and SM clock: time x MHz tells a slow-clocked GPU from an uneven split of the work
+    mine = torch.tensor([my_ms, float(clocks.summary()["sm_mhz"] or 0)], dtype=torch.float64, device=dev)
+    per_rank = [mine.clone() for _ in range(world)]
+    if world > 1:
+        torch.distributed.all_gather(per_rank, mine)
     if rank != 0:
         return None
     peaks = measured_peaks()
     tflops = wl.encoder_flops(cfg, n_load, cfg.batch) / (ms * 1e-3) / 1e12
+    parity = encoder_parity(layers, cfg, wl.encoder_input(cfg, (0, 1)), dev, depth_report=(world == 1 and not args.no_depth_report))
     return {"metric": "BERT encoder tokens/s", "value": cfg.batch * cfg.seq_len / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
             "steps": steps, "warmup": warmup, "scaling": "strong", "workload": cfg.name, "global_batch": cfg.batch, "seq_len": cfg.seq_len,
             "layers": cfg.layers, "load_blocks": n_load, "tflops_all_gpus": tflops,
-            "frac_of_sustained_peak_per_gpu": tflops / world / peaks["tflops_sustained"], "gpu_launches": steps * cfg.layers * 7}
+            "frac_of_sustained_peak_per_gpu": tflops / world / peaks["tflops_sustained"], "gpu_launches": steps * cfg.layers * 7,
+            "per_rank": [{"ms_per_step": float(t[0]), "sm_mhz_median": float(t[1]), "ms_x_ghz": float(t[0] * t[1] / 1e3)} for t in per_rank],
+            "clocks": clocks.summary(), "parity_first_layer": parity}
 
 
 def run_encoder(args, rank, world, local):
@@ -469,6 +648,7 @@ def main():
     ap.add_argument("--workload", default="attention", choices=["attention", "encoder"])
     ap.add_argument("--batch", type=int, default=0, help="override the batch size (profiling aid: smaller captures)")
     ap.add_argument("--no-encoder", action="store_true", help="skip the BERT-large encoder forward that the attention run reports under 'encoder'")
+    ap.add_argument("--no-depth-report", action="store_true", help="skip the 24-layer parity figure of the encoder sub-record (a minute of CPU work)")
     ap.add_argument("--kernel-only", action="store_true", help="skip the end-to-end and CPU-baseline legs (profiling aid)")
     ap.add_argument("--config", default=None, help="cfg2 (default) or cfg3 for attention; cfg5 (default) or cfg4 for the encoder")
     args = ap.parse_args()

@@ -80,8 +80,12 @@ int stof_mask_fill(const void* mask, int mask_dtype, int seq_len, int block_m, i
  *    `col_capacity` entries each and `part_block_mask` holds `part_capacity` tiles; entries beyond a
  *    capacity are dropped, and `counts` ({n_full, n_part, n_load, nnz_elements}, device) tells the caller
  *    afterwards whether anything was.  Capacities of (S/block_m)*(S/block_n) never drop anything.
- *  - The first call on a device looks up the array's device address (one runtime query, cached); make that
- *    first call outside any stream capture.
+ *  - The first call on a device looks up the array's device address (one runtime query, cached per device).
+ *    With the CUDA runtime's lazy module loading that query can be the moment the runtime loads the library's
+ *    device image - the 1 MiB array included - onto that device, so this one call may take device memory and
+ *    time that later calls do not; make it during set-up and outside any stream capture.  The cached address
+ *    belongs to the device's primary context: after cudaDeviceReset() on that device it is stale and the entry
+ *    point must not be used again in that process.
  *  - All calls share the one array and it keeps the previous call's bytes.  The call clears what has to
  *    start at zero itself, but two calls whose kernels overlap on the GPU (different streams, or several
  *    host threads) race on it: serialise them. */
@@ -186,15 +190,31 @@ int stof_gemm_bias_act(const void* a, long long lda, const void* w, long long ld
                        int m, int n, int k, int epilogue, int* status_dev, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * GEMM with the LayerNorm in its epilogue:  c = LN(a @ w + bias + residual) * gamma + beta, rows normalised over
+ * all n columns (biased variance, fp32 statistics taken on the fp32 sums, before any rounding to fp16).
+ * Replaces: triton_matmul_bias_layernorm, src/triton_template/gemm_add_layernorm.py:77-144 (statistics inside the
+ *           GEMM kernel), and matmul + bias + residual + F.layer_norm of src/benchmk_end2end.py:73-76, 83-86.
+ * bias, residual, gamma, beta may be NULL (0 / 0 / 1 / 0).  For n a multiple of 256 up to 1024 and k <= 2048
+ * this is ONE kernel (the n / 256 thread blocks of a row block form a cluster and exchange row statistics
+ * through distributed shared memory); other shapes run stof_gemm_bias_act followed by
+ * stof_bias_residual_layernorm in place (for long contractions that is the faster of the two, measured).
+ * ------------------------------------------------------------------------------------------ */
+int stof_gemm_bias_residual_layernorm(const void* a, long long lda, const void* w, long long ldw, const void* bias,
+                                      const void* residual, long long ldr, const void* gamma, const void* beta, float eps,
+                                      void* c, long long ldc, int m, int n, int k, int* status_dev, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Row LayerNorm with fused bias / residual add:  y = LN(x + bias + residual) * gamma + beta.
  * Replaces: triton_batched_bias_layernorm, src/triton_template/add_layernorm.py:19-107, and the
  *           normalisation half of triton_matmul_bias_layernorm (gemm_add_layernorm.py:113-123).
  * x, residual, y: (rows, hidden) fp16 with row strides in elements; bias/gamma/beta: fp16 (hidden) or
  * NULL (0 / 1 / 0).  Statistics in fp32, biased variance.  hidden a multiple of 8, at most 8192.
+ * status_dev (device int, may be NULL): a warp whose row copy does not arrive within the wait budget writes
+ * a STATUS_WAIT_TIMEOUT code there and leaves its remaining rows unwritten.
  * ------------------------------------------------------------------------------------------ */
 int stof_bias_residual_layernorm(const void* x, long long ldx, const void* bias, const void* residual, long long ldr,
                                  const void* gamma, const void* beta, float eps, void* y, long long ldy,
-                                 int rows, int hidden, void* stream);
+                                 int rows, int hidden, int* status_dev, void* stream);
 
 #ifdef __cplusplus
 }

@@ -1,28 +1,31 @@
 // Block-masked multi-head attention for sm_100a: TMA-fed tcgen05 MMAs with the accumulators in tensor
 // memory, online softmax in registers, only listed K/V blocks ever loaded.
 //
-// Tiling.  A work item is 128 query rows of one (batch, head); it walks the union of the 64-wide K/V
-// tiles that any of its row blocks lists.  Block sizes 16..128 are mapped onto this 128 x 64 tiling by a
-// PLAN built once per block index (plan_kernel): per query tile the ordered tile list and, per tile, one
-// code for each 16-row x 16-column group (0 absent, 1 full, 2+i partial tile i of the row block).
+// Tiling.  A work item is a PAIR of 64-row halves of one (batch, head) - two 64-row stretches of the sequence, neighbours
+// by default.  Each half walks its own list of 64-wide K/V tiles (the tiles any of its row blocks lists): all products are
+// M = 64 tcgen05 MMAs, whose 64 accumulator rows occupy lanes 0-15 of each 32-lane quarter of tensor memory; half A's
+// products are placed there and half B's 16 lanes further up, so that together they fill the 128 lanes and every softmax
+// warp (one quarter: 16 rows of A, 16 rows of B) has work at every step, whatever the two lists have in common.  Step j of
+// an item works on tile A[j] for half A and tile B[j] for half B; tiles both halves list come first, at the same step, and
+// are loaded once, and such a step runs as ONE M = 128 product on a copy of Q whose rows are interleaved the way the lanes are
+// (full tensor-core rate; M = 64 products take the time of M = 128 ones).  Block sizes 16..128 are mapped onto this tiling by a PLAN built once per block index (plan_kernel): per
+// item the two tile lists step by step and, per step, one code for each 16-row x 16-column group (0 absent, 1 full, 2+i
+// partial tile i of the row block).
 //
-// Kernel.  Persistent, two thread blocks per SM, static schedule over the items (heavy query tiles first inside groups of
+// Kernel.  Persistent, two thread blocks per SM, static schedule over the items (heavy items first inside groups of
 // (batch, head) pairs small enough to keep their K/V in L2, dealt round-robin; or a table made by the caller that balances the
-// tile counts over the thread blocks).
-//   warp 4      TMA producer: Q tile of the next item (double-buffered), K tiles through a ring of four slots, V tiles through
-//               a ring of three
-//   warp 5      MMA issuer:   S = Q K^T (128 x 64 x 64) into one of THREE S buffers in tensor memory, up to three tiles ahead
-//               of the PV products; O += P V with P read back from tensor memory (fp16) and V consumed in its natural
-//               key-row-major layout through an MN-major descriptor
+// step counts over the thread blocks).
+//   warp 4      TMA producer: Q of the next item (its two 64-row halves, and the same rows interleaved), K tiles through a ring of four slots, V
+//               tiles through a ring of three (one slot per step when both halves use the same tile, else two)
+//   warp 5      MMA issuer:   S = Q K^T (64 x 64 x 64 per half) into one of THREE S buffers in tensor memory, up to three steps
+//               ahead of the PV products; O += P V per half with P read back from tensor memory (fp16) and V consumed in its
+//               natural key-row-major layout through an MN-major descriptor
 //   warps 0-3   softmax: one query row per thread (tensor-memory lane): tcgen05.ld of the scores, masking from the plan
 //               codes, row maximum (3-input max), exp2 with scale and maximum folded into packed FMAs (part of the
 //               exponentials on the FMA pipe by polynomial), lazy rescale of O (only when the maximum grew by more than
 //               2^8), P written with tcgen05.st, final O / l normalisation staged in shared memory and written with TMA stores
-// The M = 128 tile covers two 64-row mask blocks; a key tile that only one of them lists keeps only half of the softmax warps
-// busy (the others store P = 0 at once and move on).  With three S buffers the two halves may drift up to three tiles apart,
-// so a run of tiles listed alternately by the upper and the lower block is worked on by both halves at the same time.
-// Masking of partial tiles and the rescale of O are out-of-line functions that work on tensor memory in place.
-// Tiles nobody lists are never loaded.
+// With three S buffers the QK^T products run ahead of the softmax warps.  Masking of partial tiles and the rescale of O are
+// out-of-line functions that work on tensor memory in place.  Tiles nobody lists are never loaded.
 #include "stof_host.h"
 #include "stof_ptx.cuh"
 
@@ -30,26 +33,50 @@ namespace stof {
 namespace {
 
 constexpr int A_TQ = 128, A_TKV = 64, A_D = 64;
-constexpr int A_SBUF = 3;                         // S buffers in tensor memory: QK^T runs up to three tiles ahead of PV
-constexpr int A_KSLOTS = 4, A_VSLOTS = 3;         // K ring (tiles g+1..g+3 and one in flight) and V ring
-constexpr int A_Q_BYTES = A_TQ * A_D * 2;         // 16 KB per Q buffer
+constexpr int A_HALF = 64;                        // rows of one half (one M = 64 product)
+#ifndef A_SBUF_N
+#define A_SBUF_N 3
+#endif
+#ifndef A_KSLOTS_N
+#define A_KSLOTS_N 4
+#endif
+#ifndef A_VSLOTS_N
+#define A_VSLOTS_N 3
+#endif
+#ifndef A_QBUFS_N
+#define A_QBUFS_N 1
+#endif
+constexpr int A_SBUF = A_SBUF_N;                  // S buffers in tensor memory: QK^T runs up to this many steps ahead of PV
+constexpr int A_KSLOTS = A_KSLOTS_N, A_VSLOTS = A_VSLOTS_N;   // K and V rings (a step takes one slot of each, or two)
+constexpr int A_QBUFS = A_QBUFS_N;                // Q buffers (items in flight on the QK^T side)
+// "tile(s) of step s have landed" barriers are counted per STEP (one wait per step for the MMA issuer, whether the step brought
+// one tile or two), "slot free" barriers per ring slot.  A full barrier is armed again A_FBARS steps later; by then its ring
+// slots have been handed back, which the issuer does only after it has seen the barrier complete: A_FBARS >= ring slots.
+constexpr int A_FBARS = A_KSLOTS > A_VSLOTS ? A_KSLOTS : A_VSLOTS;
+constexpr int A_Q_BYTES = A_TQ * A_D * 2;         // 16 KB: the two halves of an item, 8 KB each
+// A Q buffer holds the item's rows twice: half A then half B (the operands of the per-half M = 64 products), and the same rows
+// interleaved in chunks of 16 - A0-15, B0-15, A16-31, ... - which as the operand of ONE M = 128 product puts every row into the
+// tensor-memory lane the per-half products put it in; steps in which both halves work on the same key tile use that form.
+constexpr int A_QBUF_BYTES = 2 * A_Q_BYTES;
 constexpr int A_KV_BYTES = A_TKV * A_D * 2;       // 8 KB per K or V tile
 constexpr int A_OSTAGE_BYTES = 32 * A_D * 2;     // 4 KB output staging per softmax warp (TMA store source)
 constexpr int A_THREADS = 192;
 constexpr int A_CTAS_PER_SM = 2;
 constexpr int A_TMEM_COLS = 256;
-constexpr int A_COL_S = 0, A_COL_O = 192;         // S0 @0, S1 @64, S2 @128 (P overlays the first 32 columns of its S), O @192
+constexpr int A_COL_S = 0, A_COL_O = A_SBUF * A_TKV;         // S0 @0, S1 @64, S2 @128 (P overlays the first 32 columns of its S), O @192
+constexpr uint32_t A_LANE_B = 16u << 16;          // tensor-memory address offset of half B's lanes inside each quarter
 constexpr int A_MAX_TABLE_BYTES = 48 * 1024;
 constexpr float A_RESCALE_THRESHOLD = 8.0f;       // log2 units
 #ifndef A_POLY_PAIRS
 #define A_POLY_PAIRS 2                            // of every 8 column pairs, this many take the polynomial exp2
 #endif
 constexpr int A_GROUP_BH = 40;                    // (batch, head) pairs per scheduling group: 40 x 2 x S x 128 B of K/V stay in L2
+constexpr unsigned A_NO_TILE = 0xFFFFu;           // "this half has no tile at this step"
 
 enum {
-    AB_Q_FULL = 0, AB_Q_EMPTY = 2, AB_O_FREE = 4, AB_S_FULL = 5, AB_P_FULL = AB_S_FULL + A_SBUF, AB_PV_DONE = AB_P_FULL + A_SBUF,
-    AB_K_FULL = AB_PV_DONE + A_SBUF, AB_K_EMPTY = AB_K_FULL + A_KSLOTS, AB_V_FULL = AB_K_EMPTY + A_KSLOTS,
-    AB_V_EMPTY = AB_V_FULL + A_VSLOTS, AB_COUNT = AB_V_EMPTY + A_VSLOTS
+    AB_Q_FULL = 0, AB_Q_EMPTY = A_QBUFS, AB_O_FREE = 2 * A_QBUFS, AB_S_FULL = AB_O_FREE + 1, AB_P_FULL = AB_S_FULL + A_SBUF, AB_PV_DONE = AB_P_FULL + A_SBUF,
+    AB_K_FULL = AB_PV_DONE + A_SBUF, AB_K_EMPTY = AB_K_FULL + A_FBARS, AB_V_FULL = AB_K_EMPTY + A_KSLOTS,
+    AB_V_EMPTY = AB_V_FULL + A_FBARS, AB_COUNT = AB_V_EMPTY + A_VSLOTS
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -57,36 +84,40 @@ enum {
 // ---------------------------------------------------------------------------------------------
 struct PlanHeader {
     int magic, seq_len, bm, bn;
-    int n_qtiles, max_tiles, total_steps, reserved;
+    int n_qtiles, max_steps, total_steps, reserved;
 };
-constexpr int PLAN_MAGIC = 0x53544F46;
-__host__ __device__ inline size_t plan_off_ntiles() { return sizeof(PlanHeader); }
-__host__ __device__ inline size_t plan_off_order(int nqt) { return plan_off_ntiles() + ((static_cast<size_t>(nqt) * 4 + 15) & ~static_cast<size_t>(15)); }
-__host__ __device__ inline size_t plan_off_tiles(int nqt) { return plan_off_order(nqt) + ((static_cast<size_t>(nqt) * 8 + 15) & ~static_cast<size_t>(15)); }
-__host__ __device__ inline size_t plan_off_codes(int nqt, int maxt) {
-    return plan_off_tiles(nqt) + ((static_cast<size_t>(nqt) * maxt * 2 + 15) & ~static_cast<size_t>(15));
+constexpr int PLAN_MAGIC = 0x53544F47;
+__host__ __device__ inline size_t plan_off_nsteps() { return sizeof(PlanHeader); }
+__host__ __device__ inline size_t plan_off_order(int nqt) { return plan_off_nsteps() + ((static_cast<size_t>(nqt) * 4 + 15) & ~static_cast<size_t>(15)); }
+// per (item, step): tile of half A in the low 16 bits, tile of half B in the high 16 bits (A_NO_TILE: none)
+__host__ __device__ inline size_t plan_off_steps(int nqt) { return plan_off_order(nqt) + ((static_cast<size_t>(nqt) * 8 + 15) & ~static_cast<size_t>(15)); }
+__host__ __device__ inline size_t plan_off_codes(int nqt, int maxs) {
+    return plan_off_steps(nqt) + ((static_cast<size_t>(nqt) * maxs * 4 + 15) & ~static_cast<size_t>(15));
 }
-// first sequence row of the two 64-row halves of each query tile (int2; y = -1 when the tile has one half only)
-__host__ __device__ inline size_t plan_off_halves(int nqt, int maxt) { return plan_off_codes(nqt, maxt) + static_cast<size_t>(nqt) * maxt * 64; }
-__host__ __device__ inline size_t plan_total_bytes(int nqt, int maxt) {
-    return plan_off_halves(nqt, maxt) + ((static_cast<size_t>(nqt) * 8 + 15) & ~static_cast<size_t>(15));
+// first sequence row of the two 64-row halves of each item (int2; y = -1 when the item has one half only)
+__host__ __device__ inline size_t plan_off_halves(int nqt, int maxs) { return plan_off_codes(nqt, maxs) + static_cast<size_t>(nqt) * maxs * 64; }
+__host__ __device__ inline size_t plan_total_bytes(int nqt, int maxs) {
+    return plan_off_halves(nqt, maxs) + ((static_cast<size_t>(nqt) * 8 + 15) & ~static_cast<size_t>(15));
 }
 
-// One thread block per query tile: code table in shared memory -> ordered tile list + 8x4 group codes per tile.
-// A query tile is two 64-row halves of the sequence: halves 2t and 2t + 1 by default, or the two that `pairs` names for
-// it (a caller pairs halves whose key tile lists agree, so that fewer warps idle on tiles only one half lists).
-// The last block to finish ranks the query tiles by tile count (descending, stable) for the scheduler.
+// One thread block per item: code table in shared memory -> the two halves' tile lists, aligned step by step, + 8x4 group
+// codes per step.  An item is two 64-row halves of the sequence: halves 2t and 2t + 1 by default, or the two that `pairs`
+// names for it (a caller pairs halves with equally long lists, so that neither waits for the other).
+// The last block to finish ranks the items by step count (descending, stable) for the scheduler.
 __global__ void __launch_bounds__(256)
 plan_kernel(const int* __restrict__ full_row_ptr, const int* __restrict__ full_col_idx, const int* __restrict__ part_row_ptr,
             const int* __restrict__ part_col_idx, const int2* __restrict__ pairs, int seq_len, int bm, int bn, unsigned char* plan,
             unsigned int* ticket, int* status) {
-    extern __shared__ uint16_t table[];                 // [2 halves x row blocks per half][ncb]
-    __shared__ int s_count;
+    extern __shared__ uint16_t table[];                 // [2 halves x row blocks per half][ncb], then three tile lists of maxt entries
+    __shared__ int s_ns, s_na, s_nb;
     __shared__ bool s_last;
     const int nqt = gridDim.x, maxt = (seq_len + A_TKV - 1) / A_TKV;
     const int qt = blockIdx.x;
     const int nbm = seq_len / bm, ncb = seq_len / bn;
-    const int nrbh = bm >= 64 ? 1 : 64 / bm, nrb = 2 * nrbh;        // table rows per half, per tile
+    const int nrbh = bm >= 64 ? 1 : 64 / bm, nrb = 2 * nrbh;        // table rows per half, per item
+    uint16_t* list_s = table + nrb * ncb;                           // tiles both halves list (ascending)
+    uint16_t* list_a = list_s + maxt;                               // tiles only half A lists
+    uint16_t* list_b = list_a + maxt;                               // tiles only half B lists
     const int n_half = (seq_len + 63) / 64;
     int half[2] = {2 * qt, 2 * qt + 1 < n_half ? 2 * qt + 1 : -1};
     if (pairs != nullptr) {
@@ -98,9 +129,9 @@ plan_kernel(const int* __restrict__ full_row_ptr, const int* __restrict__ full_c
             half[0] = 0; half[1] = -1;
         }
     }
-    int* n_tiles = reinterpret_cast<int*>(plan + plan_off_ntiles());
-    int2* order = reinterpret_cast<int2*>(plan + plan_off_order(nqt));     // per rank: {query tile, tile count}
-    uint16_t* tiles = reinterpret_cast<uint16_t*>(plan + plan_off_tiles(nqt)) + static_cast<size_t>(qt) * maxt;
+    int* n_steps = reinterpret_cast<int*>(plan + plan_off_nsteps());
+    int2* order = reinterpret_cast<int2*>(plan + plan_off_order(nqt));     // per rank: {item, step count}
+    uint32_t* steps = reinterpret_cast<uint32_t*>(plan + plan_off_steps(nqt)) + static_cast<size_t>(qt) * maxt;
     uint16_t* codes = reinterpret_cast<uint16_t*>(plan + plan_off_codes(nqt, maxt)) + static_cast<size_t>(qt) * maxt * 32;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
@@ -126,55 +157,77 @@ plan_kernel(const int* __restrict__ full_row_ptr, const int* __restrict__ full_c
     }
     __syncthreads();
     if (warp == 0) {
-        int count = 0;
+        int ns = 0, na = 0, nb = 0;
         for (int t0 = 0; t0 < maxt; t0 += 32) {
             const int t = t0 + lane;
-            bool active = false;
+            bool act[2] = {false, false};
             if (t < maxt) {
                 const int c_lo = (t * A_TKV) / bn;
                 const int c_hi = min(ncb - 1, (t * A_TKV + A_TKV - 1) / bn);
                 for (int lrb = 0; lrb < nrb; ++lrb)
-                    for (int c = c_lo; c <= c_hi; ++c) active |= table[lrb * ncb + c] != 0;
+                    for (int c = c_lo; c <= c_hi; ++c) act[lrb / nrbh] |= table[lrb * ncb + c] != 0;
             }
-            const unsigned bal = __ballot_sync(0xffffffffu, active);
-            if (active) tiles[count + __popc(bal & ((1u << lane) - 1u))] = static_cast<uint16_t>(t);
-            count += __popc(bal);
+            const unsigned lower = (1u << lane) - 1u;
+            const unsigned bal_s = __ballot_sync(0xffffffffu, act[0] && act[1]);
+            const unsigned bal_a = __ballot_sync(0xffffffffu, act[0] && !act[1]);
+            const unsigned bal_b = __ballot_sync(0xffffffffu, !act[0] && act[1]);
+            if (act[0] && act[1]) list_s[ns + __popc(bal_s & lower)] = static_cast<uint16_t>(t);
+            if (act[0] && !act[1]) list_a[na + __popc(bal_a & lower)] = static_cast<uint16_t>(t);
+            if (!act[0] && act[1]) list_b[nb + __popc(bal_b & lower)] = static_cast<uint16_t>(t);
+            ns += __popc(bal_s);
+            na += __popc(bal_a);
+            nb += __popc(bal_b);
         }
         if (lane == 0) {
-            s_count = count;
-            n_tiles[qt] = count;
+            s_ns = ns; s_na = na; s_nb = nb;
+            n_steps[qt] = ns + max(na, nb);
         }
     }
     __syncthreads();
-    const int count = s_count;
-    // codes[j][row group 0..7][col group 0..3], 14 bits each.  The top two bits of the LAST code of a row group carry the class
-    // of the softmax warp that owns it (32 rows = two row groups x four column groups): 0 every group absent, 1 every group
-    // full, 2 anything else - the kernel then needs no warp vote to pick its path.
-    // sequence row of 16-row group rg of this tile (-1: none), and its row of the table
+    const int ns = s_ns, na = s_na, nb = s_nb;
+    const int count = ns + max(na, nb);
+    // tile of half h at step j: the tiles both halves list come first, then each half's own
+    auto step_tile = [&](int j, int h) -> unsigned {
+        if (j < ns) return list_s[j];
+        const int i = j - ns;
+        if (h == 0) return i < na ? list_a[i] : A_NO_TILE;
+        return i < nb ? list_b[i] : A_NO_TILE;
+    };
+    for (int j = threadIdx.x; j < count; j += blockDim.x) steps[j] = step_tile(j, 0) | (step_tile(j, 1) << 16);
+    // codes[j][row group 0..7][col group 0..3], 14 bits each; row group = 4 * half + quarter, i.e. the 16 rows of that half
+    // that live in softmax warp `quarter`.  The top two bits of the LAST code of a row group carry the class of that warp at
+    // this step (its two row groups x four column groups): 0 every group absent, 1 every row group either full or - its half
+    // having no tile at this step - absent, 2 anything else: the kernel then needs no warp vote to pick its path.
     auto group_row = [&](int rg) { return half[rg >> 2] < 0 ? -1 : half[rg >> 2] * 64 + (rg & 3) * 16; };
     auto table_row = [&](int rg) { return (rg >> 2) * nrbh + (bm >= 64 ? 0 : ((rg & 3) * 16) / bm); };
+    auto group_code = [&](int j, int rg, int cg) -> uint16_t {
+        const unsigned t = step_tile(j, rg >> 2);
+        if (t == A_NO_TILE) return 0;
+        const int row = group_row(rg), col = static_cast<int>(t) * A_TKV + cg * 16;
+        return (row >= 0 && row < seq_len && col < seq_len) ? table[table_row(rg) * ncb + col / bn] : uint16_t(0);
+    };
     for (int i = threadIdx.x; i < count * 32; i += blockDim.x) {
         const int j = i >> 5, rg = (i >> 2) & 7, cg = i & 3;
-        const int t = tiles[j];
-        const int row = group_row(rg), col = t * A_TKV + cg * 16;
-        uint16_t code = 0;
-        if (row >= 0 && row < seq_len && col < seq_len) code = table[table_row(rg) * ncb + col / bn];
+        uint16_t code = group_code(j, rg, cg);
         if (cg == 3) {
-            bool all0 = true, all1 = true;
-            for (int r2 = (rg & ~1); r2 < (rg & ~1) + 2; ++r2)
+            bool all0 = true, fast = true;
+            for (int r2 = (rg & 3); r2 < 8; r2 += 4) {
+                bool g0 = true, g1 = true;
                 for (int c2 = 0; c2 < 4; ++c2) {
-                    const int row2 = group_row(r2), col2 = t * A_TKV + c2 * 16;
-                    const uint16_t k2 = (row2 >= 0 && row2 < seq_len && col2 < seq_len) ? table[table_row(r2) * ncb + col2 / bn] : uint16_t(0);
-                    all0 &= k2 == 0;
-                    all1 &= k2 == 1;
+                    const uint16_t k2 = group_code(j, r2, c2);
+                    g0 &= k2 == 0;
+                    g1 &= k2 == 1;
                 }
-            code = static_cast<uint16_t>(code | ((all0 ? 0u : (all1 ? 1u : 2u)) << 14));
+                all0 &= g0;
+                fast &= g1 || (g0 && step_tile(j, r2 >> 2) == A_NO_TILE);
+            }
+            code = static_cast<uint16_t>(code | ((all0 ? 0u : (fast ? 1u : 2u)) << 14));
         }
         codes[i] = code;
     }
     if (threadIdx.x == 0)
         reinterpret_cast<int2*>(plan + plan_off_halves(nqt, maxt))[qt] = make_int2(half[0] * 64, half[1] < 0 ? -1 : half[1] * 64);
-    // the last block orders the query tiles by descending tile count (stable)
+    // the last block orders the items by descending step count (stable)
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -188,19 +241,19 @@ plan_kernel(const int* __restrict__ full_row_ptr, const int* __restrict__ full_c
         PlanHeader* h = reinterpret_cast<PlanHeader*>(plan);
         int total = 0;
         for (int a = threadIdx.x; a < nqt; a += blockDim.x) {
-            const int na = __ldcg(n_tiles + a);
+            const int na2 = __ldcg(n_steps + a);
             int rank = 0;
             for (int b = 0; b < nqt; ++b) {
-                const int nb2 = __ldcg(n_tiles + b);
-                rank += (nb2 > na || (nb2 == na && b < a)) ? 1 : 0;
+                const int nb2 = __ldcg(n_steps + b);
+                rank += (nb2 > na2 || (nb2 == na2 && b < a)) ? 1 : 0;
             }
-            order[rank] = make_int2(a, na);
-            total += na;
+            order[rank] = make_int2(a, na2);
+            total += na2;
         }
         atomicAdd(&h->total_steps, total);
         if (threadIdx.x == 0) {
             h->magic = PLAN_MAGIC; h->seq_len = seq_len; h->bm = bm; h->bn = bn;
-            h->n_qtiles = nqt; h->max_tiles = maxt; h->reserved = 0;
+            h->n_qtiles = nqt; h->max_steps = maxt; h->reserved = 0;
         }
     }
 }
@@ -214,7 +267,7 @@ struct AttnParams {
     const unsigned char* plan;
     int batch, heads, seq_len;
     int bm, bn, bm_shift, bn_shift;
-    int n_qtiles, max_tiles;
+    int n_qtiles, max_steps;
     unsigned total_items, bh_total;
     int slot_s[4], slot_h[4], slot_b[4];   // coordinate slot (1..3) of row / head / batch in the q, k, v, out tensor maps
     float scale_log2;
@@ -237,7 +290,7 @@ __device__ __forceinline__ void tma_tile_store(const CUtensorMap* map, const voi
 }
 
 // Static schedule.  Default: items are enumerated group by group ((batch, head) pairs in chunks of A_GROUP_BH), inside a
-// group query-tile-rank major (heaviest tiles first), and dealt round-robin to the thread blocks.  With a schedule table
+// group in rank order (the items with the most steps first), and dealt round-robin to the thread blocks.  With a schedule table
 // ({blocks G, G + 1 offsets, item ids = (batch * heads + head) * query tiles + query tile}, made by the caller, e.g. by a
 // longest-processing-time assignment over the tile counts) block b walks ids[offset[b] .. offset[b + 1]).
 struct Item {
@@ -269,7 +322,7 @@ __device__ __forceinline__ Item decode_item(unsigned id, const AttnParams& p, co
         }
         const unsigned bh = id / static_cast<unsigned>(p.n_qtiles);
         it.qt = static_cast<int>(id - bh * static_cast<unsigned>(p.n_qtiles));
-        it.n = __ldg(reinterpret_cast<const int*>(p.plan + plan_off_ntiles()) + it.qt);
+        it.n = __ldg(reinterpret_cast<const int*>(p.plan + plan_off_nsteps()) + it.qt);
         it.batch = static_cast<int>(bh / p.heads);
         it.head = static_cast<int>(bh - it.batch * p.heads);
         return it;
@@ -364,13 +417,49 @@ __device__ __noinline__ void rescale_o_in_tmem(uint32_t t_o, float alpha) {
     tc_wait_st();
 }
 
+// The four K = 16 products of one 64 x 64 x 64 block, issued as one instruction sequence (the issuing thread is a single lane:
+// every instruction it spends between two products delays all of them).
+// S[tmem] = Q[smem] K[smem]^T: both K-major operands advance by 32 bytes (2 in descriptor units) per product.
+__device__ __forceinline__ void mma_chain_qk(uint32_t d_tmem, uint64_t q_desc, uint64_t k_desc, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p0, p1;\n\t.reg .b64 a, b;\n\t"
+        "setp.ne.b32 p0, 0, 0;\n\t"
+        "setp.eq.b32 p1, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p0;\n\t"
+        "add.s64 a, %1, 2;\n\tadd.s64 b, %2, 2;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, p1;\n\t"
+        "add.s64 a, %1, 4;\n\tadd.s64 b, %2, 4;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, p1;\n\t"
+        "add.s64 a, %1, 6;\n\tadd.s64 b, %2, 6;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, p1;\n\t}"
+        ::"r"(d_tmem), "l"(q_desc), "l"(k_desc), "r"(idesc)
+        : "memory");
+}
+// O[tmem] (+)= P[tmem] V[smem]: P advances by 8 columns (16 fp16 keys) per product, the MN-major V by 16 key rows = 2048 bytes
+// (128 in descriptor units); `accumulate` = 0 overwrites O with the first product.
+__device__ __forceinline__ void mma_chain_pv(uint32_t o_tmem, uint32_t p_tmem, uint64_t v_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p0, p1;\n\t.reg .b64 b;\n\t.reg .b32 a;\n\t"
+        "setp.ne.b32 p0, %4, 0;\n\t"
+        "setp.eq.b32 p1, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p0;\n\t"
+        "add.u32 a, %1, 8;\n\tadd.s64 b, %2, 128;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, p1;\n\t"
+        "add.u32 a, %1, 16;\n\tadd.s64 b, %2, 256;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, p1;\n\t"
+        "add.u32 a, %1, 24;\n\tadd.s64 b, %2, 384;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, p1;\n\t}"
+        ::"r"(o_tmem), "r"(p_tmem), "l"(v_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 __global__ void __launch_bounds__(A_THREADS, A_CTAS_PER_SM)
-block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_q16, const __grid_constant__ CUtensorMap map_k,
                   const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o, const AttnParams p) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     unsigned char* q_smem = smem;                                   // 2 buffers
-    unsigned char* k_smem = q_smem + 2 * A_Q_BYTES;
+    unsigned char* k_smem = q_smem + A_QBUFS * A_QBUF_BYTES;
     unsigned char* v_smem = k_smem + A_KSLOTS * A_KV_BYTES;
     unsigned char* o_smem = v_smem + A_VSLOTS * A_KV_BYTES;          // 4 x 4 KB, one slab per softmax warp
     uint64_t* bars = reinterpret_cast<uint64_t*>(o_smem + 4 * A_OSTAGE_BYTES);
@@ -380,13 +469,15 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const WaitCtx wctx{abort_flag, p.status};
     const int2* plan_sched = reinterpret_cast<const int2*>(p.plan + plan_off_order(p.n_qtiles));
-    const uint16_t* plan_tiles = reinterpret_cast<const uint16_t*>(p.plan + plan_off_tiles(p.n_qtiles));
-    const uint16_t* plan_codes = reinterpret_cast<const uint16_t*>(p.plan + plan_off_codes(p.n_qtiles, p.max_tiles));
-    const int2* plan_halves = reinterpret_cast<const int2*>(p.plan + plan_off_halves(p.n_qtiles, p.max_tiles));
+    const uint32_t* plan_steps = reinterpret_cast<const uint32_t*>(p.plan + plan_off_steps(p.n_qtiles));
+    const uint16_t* plan_codes = reinterpret_cast<const uint16_t*>(p.plan + plan_off_codes(p.n_qtiles, p.max_steps));
+    const int2* plan_halves = reinterpret_cast<const int2*>(p.plan + plan_off_halves(p.n_qtiles, p.max_steps));
 
     if (threadIdx.x == 0) {
-        *abort_flag = (p.status != nullptr && *p.status != 0) ? 1 : 0;
-        for (int i = 0; i < 2; ++i) {
+        // a plan made for another sequence length or block shape is reported, not followed
+        const int4 ph = __ldg(reinterpret_cast<const int4*>(p.plan));
+        const int st = p.status != nullptr ? *p.status : 0;
+        for (int i = 0; i < A_QBUFS; ++i) {
             mbar_init(&bars[AB_Q_FULL + i], 1);
             mbar_init(&bars[AB_Q_EMPTY + i], 1);
         }
@@ -396,15 +487,16 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             mbar_init(&bars[AB_P_FULL + i], 4);
             mbar_init(&bars[AB_PV_DONE + i], 1);
         }
-        for (int i = 0; i < A_KSLOTS; ++i) {
+        for (int i = 0; i < A_FBARS; ++i) {
             mbar_init(&bars[AB_K_FULL + i], 1);
-            mbar_init(&bars[AB_K_EMPTY + i], 1);
-        }
-        for (int i = 0; i < A_VSLOTS; ++i) {
             mbar_init(&bars[AB_V_FULL + i], 1);
-            mbar_init(&bars[AB_V_EMPTY + i], 1);
         }
+        for (int i = 0; i < A_KSLOTS; ++i) mbar_init(&bars[AB_K_EMPTY + i], 1);
+        for (int i = 0; i < A_VSLOTS; ++i) mbar_init(&bars[AB_V_EMPTY + i], 1);
         fence_mbar_init();
+        const bool plan_ok = ph.x == PLAN_MAGIC && ph.y == p.seq_len && ph.z == p.bm && ph.w == p.bn;
+        if (!plan_ok && p.status != nullptr) atomicCAS(p.status, 0, STATUS_BAD_INDEX);
+        *abort_flag = (st != 0 || !plan_ok) ? 1 : 0;
     }
     if (warp == 5) {
         tmem_alloc(tmem_slot, A_TMEM_COLS);
@@ -420,10 +512,13 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             // -------------------------------------------------------------- TMA producer
             if (elect_one()) {
                 tma_prefetch_desc(&map_q);
+                tma_prefetch_desc(&map_q16);
                 tma_prefetch_desc(&map_k);
                 tma_prefetch_desc(&map_v);
-                // two cursors over the block's stream of steps (tiles of its items with tiles): K loads run A_SBUF steps ahead of
-                // the V loads, in the order the MMA warp consumes them.  `it` counts the items with tiles (Q buffers alternate).
+                // two cursors over the block's stream of steps (steps of its items that have any): K loads run A_SBUF steps ahead
+                // of the V loads, in the order the MMA warp consumes them.  `it` counts the items with steps (Q buffers alternate).
+                // A step takes one ring slot when both halves work on the same tile (or one of them has none), else two: first
+                // the tile of half A, then the tile of half B; all of a step's bytes are reported to the step's one barrier.
                 struct Cursor { unsigned k; Item item; int j, it; };
                 auto settle = [&](Cursor& c) {
                     for (;;) {
@@ -435,144 +530,206 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 auto advance = [&](Cursor& c) {
                     if (++c.j >= c.item.n) { c.j = 0; ++c.k; ++c.it; settle(c); }
                 };
+                auto step_word = [&](const Cursor& c) { return __ldg(plan_steps + static_cast<size_t>(c.item.qt) * p.max_steps + c.j); };
                 Cursor kc, vc;
                 kc.k = 0; kc.j = 0; kc.it = 0;
                 settle(kc);
                 vc = kc;
-                unsigned uk = 0, uv = 0;
+                unsigned uk = 0, uv = 0;                      // ring slots used so far
+                unsigned gk = 0, gv = 0;                      // steps loaded so far
                 auto load_k = [&]() {
                     if (kc.j == 0) {
-                        const int qb = kc.it & 1;
-                        mbar_wait(&bars[AB_Q_EMPTY + qb], static_cast<uint32_t>(((kc.it >> 1) & 1) ^ 1), wctx, AB_Q_EMPTY + qb);
-                        // the tile's two 64-row halves (the second may be missing; its rows then carry "absent" codes only)
+                        const int qb = kc.it % A_QBUFS;
+                        mbar_wait(&bars[AB_Q_EMPTY + qb], static_cast<uint32_t>(((kc.it / A_QBUFS) & 1) ^ 1), wctx, AB_Q_EMPTY + qb);
+                        // the item's two 64-row halves (the second may be missing; its rows then carry "absent" codes only)
                         const int2 hr = __ldg(plan_halves + kc.item.qt);
-                        mbar_arrive_expect_tx(&bars[AB_Q_FULL + qb], hr.y >= 0 ? A_Q_BYTES : A_Q_BYTES / 2);
-                        tma_tile(q_smem + qb * A_Q_BYTES, &map_q, &bars[AB_Q_FULL + qb], hr.x, kc.item.head, kc.item.batch, p.slot_s[0],
-                                 p.slot_h[0], p.slot_b[0]);
-                        if (hr.y >= 0)
-                            tma_tile(q_smem + qb * A_Q_BYTES + A_Q_BYTES / 2, &map_q, &bars[AB_Q_FULL + qb], hr.y, kc.item.head, kc.item.batch,
-                                     p.slot_s[0], p.slot_h[0], p.slot_b[0]);
+                        unsigned char* qd = q_smem + qb * A_QBUF_BYTES;
+                        uint64_t* qfull = &bars[AB_Q_FULL + qb];
+                        mbar_arrive_expect_tx(qfull, hr.y >= 0 ? A_QBUF_BYTES : A_Q_BYTES / 2);
+                        tma_tile(qd, &map_q, qfull, hr.x, kc.item.head, kc.item.batch, p.slot_s[0], p.slot_h[0], p.slot_b[0]);
+                        if (hr.y >= 0) {
+                            tma_tile(qd + A_Q_BYTES / 2, &map_q, qfull, hr.y, kc.item.head, kc.item.batch, p.slot_s[0], p.slot_h[0], p.slot_b[0]);
+                            // the interleaved copy: 16-row boxes of half A and half B in turn
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) {
+                                tma_tile(qd + A_Q_BYTES + (2 * c) * 2048, &map_q16, qfull, hr.x + 16 * c, kc.item.head, kc.item.batch, p.slot_s[0],
+                                         p.slot_h[0], p.slot_b[0]);
+                                tma_tile(qd + A_Q_BYTES + (2 * c + 1) * 2048, &map_q16, qfull, hr.y + 16 * c, kc.item.head, kc.item.batch, p.slot_s[0],
+                                         p.slot_h[0], p.slot_b[0]);
+                            }
+                        }
                     }
-                    const int sl = static_cast<int>(uk % A_KSLOTS);
-                    mbar_wait(&bars[AB_K_EMPTY + sl], ((uk / A_KSLOTS) & 1) ^ 1, wctx, AB_K_EMPTY + sl);
-                    const int tile = plan_tiles[static_cast<size_t>(kc.item.qt) * p.max_tiles + kc.j];
-                    mbar_arrive_expect_tx(&bars[AB_K_FULL + sl], A_KV_BYTES);
-                    tma_tile(k_smem + sl * A_KV_BYTES, &map_k, &bars[AB_K_FULL + sl], tile * A_TKV, kc.item.head, kc.item.batch, p.slot_s[1], p.slot_h[1],
-                             p.slot_b[1]);
+                    const uint32_t w = step_word(kc);
+                    const unsigned ta = w & 0xFFFFu, tb = w >> 16;
+                    const unsigned first = ta != A_NO_TILE ? ta : tb;
+                    const int tiles = (ta != A_NO_TILE && tb != A_NO_TILE && ta != tb) ? 2 : 1;
+                    uint64_t* full = &bars[AB_K_FULL + gk % A_FBARS];
+                    for (int i = 0; i < tiles; ++i, ++uk) {
+                        const int sl = static_cast<int>(uk % A_KSLOTS);
+                        mbar_wait(&bars[AB_K_EMPTY + sl], ((uk / A_KSLOTS) & 1) ^ 1, wctx, AB_K_EMPTY + sl);
+                        if (i == 0) mbar_arrive_expect_tx(full, tiles * A_KV_BYTES);
+                        tma_tile(k_smem + sl * A_KV_BYTES, &map_k, full, static_cast<int>(i == 0 ? first : tb) * A_TKV, kc.item.head,
+                                 kc.item.batch, p.slot_s[1], p.slot_h[1], p.slot_b[1]);
+                    }
+                    ++gk;
                     advance(kc);
-                    ++uk;
                 };
                 for (int i = 0; i < A_SBUF && kc.item.valid; ++i) load_k();
                 while (vc.item.valid) {
-                    const int sl = static_cast<int>(uv % A_VSLOTS);
-                    mbar_wait(&bars[AB_V_EMPTY + sl], ((uv / A_VSLOTS) & 1) ^ 1, wctx, AB_V_EMPTY + sl);
-                    const int tile = plan_tiles[static_cast<size_t>(vc.item.qt) * p.max_tiles + vc.j];
-                    mbar_arrive_expect_tx(&bars[AB_V_FULL + sl], A_KV_BYTES);
-                    tma_tile(v_smem + sl * A_KV_BYTES, &map_v, &bars[AB_V_FULL + sl], tile * A_TKV, vc.item.head, vc.item.batch, p.slot_s[2], p.slot_h[2],
-                             p.slot_b[2]);
+                    const uint32_t w = step_word(vc);
+                    const unsigned ta = w & 0xFFFFu, tb = w >> 16;
+                    const unsigned first = ta != A_NO_TILE ? ta : tb;
+                    const int tiles = (ta != A_NO_TILE && tb != A_NO_TILE && ta != tb) ? 2 : 1;
+                    uint64_t* full = &bars[AB_V_FULL + gv % A_FBARS];
+                    for (int i = 0; i < tiles; ++i, ++uv) {
+                        const int sl = static_cast<int>(uv % A_VSLOTS);
+                        mbar_wait(&bars[AB_V_EMPTY + sl], ((uv / A_VSLOTS) & 1) ^ 1, wctx, AB_V_EMPTY + sl);
+                        if (i == 0) mbar_arrive_expect_tx(full, tiles * A_KV_BYTES);
+                        tma_tile(v_smem + sl * A_KV_BYTES, &map_v, full, static_cast<int>(i == 0 ? first : tb) * A_TKV, vc.item.head,
+                                 vc.item.batch, p.slot_s[2], p.slot_h[2], p.slot_b[2]);
+                    }
+                    ++gv;
                     advance(vc);
-                    ++uv;
                     if (kc.item.valid) load_k();
                 }
             }
         } else if (warp == 5) {
             // -------------------------------------------------------------- MMA issuer
             if (elect_one()) {
-                constexpr uint32_t idesc_qk = make_idesc_f16(A_TQ, A_TKV, /*b_mn_major=*/false);
-                constexpr uint32_t idesc_pv = make_idesc_f16(A_TQ, A_D, /*b_mn_major=*/true);
-                // two cursors over the same stream of steps: the QK^T cursor runs A_SBUF steps ahead of the PV cursor
-                struct Cursor { unsigned k; int n, j, it; bool valid; };
+                constexpr uint32_t idesc_qk = make_idesc_f16(A_HALF, A_TKV, /*b_mn_major=*/false);
+                constexpr uint32_t idesc_pv = make_idesc_f16(A_HALF, A_D, /*b_mn_major=*/true);
+                constexpr uint32_t idesc_qk2 = make_idesc_f16(A_TQ, A_TKV, /*b_mn_major=*/false);     // both halves in one product
+                constexpr uint32_t idesc_pv2 = make_idesc_f16(A_TQ, A_D, /*b_mn_major=*/true);
+                // shared-memory descriptors of buffer 0 / slot 0; the others follow by adding their byte offset / 16
+                const uint64_t q_desc0 = make_smem_desc_sw128(smem_u32(q_smem), 16, 1024);
+                const uint64_t k_desc0 = make_smem_desc_sw128(smem_u32(k_smem), 16, 1024);
+                const uint64_t v_desc0 = make_smem_desc_sw128(smem_u32(v_smem), 16, 1024);
+                // two cursors over the same stream of steps: the QK^T cursor runs A_SBUF steps ahead of the PV cursor.  The step
+                // word of a cursor's position is requested as soon as the cursor gets there, a whole step before it is needed.
+                struct Cursor { unsigned k; int qt, n, j, it; bool valid; uint32_t word; };
                 auto settle = [&](Cursor& c) {
                     for (;;) {
                         const Item item = fetch_item(c.k, p, plan_sched);
                         c.valid = item.valid;
                         c.n = item.n;
-                        if (!item.valid || item.n > 0) return;
+                        c.qt = item.qt;
+                        if (!item.valid || item.n > 0) break;
                         ++c.k;
                     }
+                    if (c.valid) c.word = __ldg(plan_steps + static_cast<size_t>(c.qt) * p.max_steps);
                 };
                 auto advance = [&](Cursor& c) {
                     if (++c.j >= c.n) { c.j = 0; ++c.k; ++c.it; settle(c); }
+                    else c.word = __ldg(plan_steps + static_cast<size_t>(c.qt) * p.max_steps + c.j);
                 };
                 Cursor qk, pv;
-                qk.k = 0; qk.j = 0; qk.it = 0;
+                qk.k = 0; qk.j = 0; qk.it = 0; qk.word = 0;
                 settle(qk);
                 pv = qk;
-                unsigned uq = 0, u = 0;
-                // S = Q K^T of step uq into buffer uq % A_SBUF.  The buffer held S and P of step uq - A_SBUF: the PV product that read
-                // that P was issued before and the tensor core executes this thread's MMAs in order.
+                unsigned gq = 0, g = 0;                       // steps issued: QK^T, PV
+                unsigned uq = 0, uv = 0;                      // ring slots consumed: K, V
+                // S = Q K^T of step gq into buffer gq % A_SBUF, half A in lanes 0-15 of each quarter, half B in lanes 16-31.  The
+                // buffer held S and P of step gq - A_SBUF: the PV products that read that P were issued before and the tensor core
+                // executes this thread's MMAs in order.
                 auto issue_qk = [&]() {
-                    const int qb = qk.it & 1;
-                    if (qk.j == 0) mbar_wait(&bars[AB_Q_FULL + qb], static_cast<uint32_t>((qk.it >> 1) & 1), wctx, AB_Q_FULL + qb);
-                    const int sl = static_cast<int>(uq % A_KSLOTS);
-                    mbar_wait(&bars[AB_K_FULL + sl], (uq / A_KSLOTS) & 1, wctx, AB_K_FULL + sl);
+                    const int qb = qk.it % A_QBUFS;
+                    if (qk.j == 0) mbar_wait(&bars[AB_Q_FULL + qb], static_cast<uint32_t>((qk.it / A_QBUFS) & 1), wctx, AB_Q_FULL + qb);
+                    const uint32_t w = qk.word;
+                    const unsigned ta = w & 0xFFFFu, tb = w >> 16;
+                    const bool two = ta != A_NO_TILE && tb != A_NO_TILE && ta != tb;
+                    const int sl0 = static_cast<int>(uq % A_KSLOTS), sl1 = static_cast<int>((uq + 1) % A_KSLOTS);
+                    const int fb = static_cast<int>(gq % A_FBARS);
+                    mbar_wait(&bars[AB_K_FULL + fb], (gq / A_FBARS) & 1, wctx, AB_K_FULL + fb);
                     tc_fence_after();
-                    const uint32_t q_addr = smem_u32(q_smem + qb * A_Q_BYTES);
-                    const uint32_t k_addr = smem_u32(k_smem + sl * A_KV_BYTES);
-                    const int sb = static_cast<int>(uq % A_SBUF);
+                    const uint64_t qd = q_desc0 + static_cast<uint64_t>(qb * (A_QBUF_BYTES >> 4));
+                    const int sb = static_cast<int>(gq % A_SBUF);
                     const uint32_t d = tmem_base + A_COL_S + sb * A_TKV;
-#pragma unroll
-                    for (int kk = 0; kk < A_D / 16; ++kk)
-                        mma_f16_ss(d, make_smem_desc_sw128(q_addr + kk * 32, 16, 1024), make_smem_desc_sw128(k_addr + kk * 32, 16, 1024),
-                                   idesc_qk, kk > 0 ? 1u : 0u);
-                    tc_commit(&bars[AB_K_EMPTY + sl]);
+                    const uint64_t kd0 = k_desc0 + static_cast<uint64_t>(sl0 * (A_KV_BYTES >> 4));
+                    if (ta == tb) {
+                        mma_chain_qk(d, qd + (A_Q_BYTES >> 4), kd0, idesc_qk2);        // the interleaved rows: one M = 128 product chain
+                    } else {
+                        if (ta != A_NO_TILE) mma_chain_qk(d, qd, kd0, idesc_qk);
+                        if (tb != A_NO_TILE)
+                            mma_chain_qk(d + A_LANE_B, qd + (A_Q_BYTES >> 5), two ? k_desc0 + static_cast<uint64_t>(sl1 * (A_KV_BYTES >> 4)) : kd0, idesc_qk);
+                    }
+                    tc_commit(&bars[AB_K_EMPTY + sl0]);
+                    if (two) tc_commit(&bars[AB_K_EMPTY + sl1]);
                     tc_commit(&bars[AB_S_FULL + sb]);
                     if (qk.j == qk.n - 1) tc_commit(&bars[AB_Q_EMPTY + qb]);     // every QK^T of that item has been issued
                     advance(qk);
-                    ++uq;
+                    ++gq;
+                    uq += two ? 2u : 1u;
                 };
                 for (int i = 0; i < A_SBUF && qk.valid; ++i) issue_qk();
                 while (pv.valid) {
                     if (pv.j == 0) mbar_wait(&bars[AB_O_FREE], static_cast<uint32_t>((pv.it & 1) ^ 1), wctx, AB_O_FREE);     // the previous item's O was read
-                    const int sb = static_cast<int>(u % A_SBUF), sl = static_cast<int>(u % A_VSLOTS);
-                    mbar_wait(&bars[AB_V_FULL + sl], (u / A_VSLOTS) & 1, wctx, AB_V_FULL + sl);      // long there: off the P -> PV path
-                    mbar_wait(&bars[AB_P_FULL + sb], (u / A_SBUF) & 1, wctx, AB_P_FULL + sb);
+                    const uint32_t w = pv.word;
+                    const unsigned ta = w & 0xFFFFu, tb = w >> 16;
+                    const bool two = ta != A_NO_TILE && tb != A_NO_TILE && ta != tb;
+                    const int sb = static_cast<int>(g % A_SBUF);
+                    const int sl0 = static_cast<int>(uv % A_VSLOTS), sl1 = static_cast<int>((uv + 1) % A_VSLOTS);
+                    const int fb = static_cast<int>(g % A_FBARS);
+                    mbar_wait(&bars[AB_V_FULL + fb], (g / A_FBARS) & 1, wctx, AB_V_FULL + fb);      // long there: off the P -> PV path
+                    mbar_wait(&bars[AB_P_FULL + sb], (g / A_SBUF) & 1, wctx, AB_P_FULL + sb);
                     tc_fence_after();
-                    const uint32_t v_addr = smem_u32(v_smem + sl * A_KV_BYTES);
                     const uint32_t p_tmem = tmem_base + A_COL_S + sb * A_TKV;
-#pragma unroll
-                    for (int kk = 0; kk < A_TKV / 16; ++kk)
-                        mma_f16_ts(tmem_base + A_COL_O, p_tmem + kk * 8, make_smem_desc_sw128(v_addr + kk * 2048, 16, 1024), idesc_pv,
-                                   (pv.j > 0 || kk > 0) ? 1u : 0u);
-                    tc_commit(&bars[AB_V_EMPTY + sl]);
+                    const uint32_t acc = pv.j > 0 ? 1u : 0u;
+                    // a half's steps are the first ones of the item, so its first product (which overwrites O) comes at step 0
+                    const uint64_t vd0 = v_desc0 + static_cast<uint64_t>(sl0 * (A_KV_BYTES >> 4));
+                    if (ta == tb) {
+                        mma_chain_pv(tmem_base + A_COL_O, p_tmem, vd0, idesc_pv2, acc);
+                    } else {
+                        if (ta != A_NO_TILE) mma_chain_pv(tmem_base + A_COL_O, p_tmem, vd0, idesc_pv, acc);
+                        if (tb != A_NO_TILE)
+                            mma_chain_pv(tmem_base + A_COL_O + A_LANE_B, p_tmem + A_LANE_B,
+                                         two ? v_desc0 + static_cast<uint64_t>(sl1 * (A_KV_BYTES >> 4)) : vd0, idesc_pv, acc);
+                    }
+                    tc_commit(&bars[AB_V_EMPTY + sl0]);
+                    if (two) tc_commit(&bars[AB_V_EMPTY + sl1]);
                     tc_commit(&bars[AB_PV_DONE + sb]);
                     advance(pv);
-                    ++u;
+                    ++g;
+                    uv += two ? 2u : 1u;
                     if (qk.valid) issue_qk();                                     // into the buffer this PV has just been issued for
                 }
             }
         } else {
             // -------------------------------------------------------------- softmax warps (one row per thread)
-            const int lr = warp * 32 + lane;                 // local row = tensor-memory lane
+            // lanes 0-15 of the warp own rows 16 * warp .. + 15 of half A, lanes 16-31 the same rows of half B
+            const int hsel = lane >> 4;                      // which half this thread's row belongs to
+            const int rih = warp * 16 + (lane & 15);         // row inside the half
             const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-            const int rg = lr >> 4;                          // 16-row group inside the query tile
+            const int rg = hsel * 4 + warp;                  // 16-row group of the plan codes
             const float scale = p.scale_log2, inv_scale = 1.0f / p.scale_log2;
             unsigned g = 0;                                  // steps of this block so far (matches the MMA warp's count)
+            int sbuf = 0;                                    // g % A_SBUF and (g / A_SBUF) & 1, kept as running values
+            uint32_t sphase = 0;
             // per-item values that need global loads are fetched one item ahead (no dependent-load chain at item boundaries)
-            // first sequence row of the 64-row half this warp works on (-1: the tile has no such half)
+            // first sequence row of the 64-row half this thread works on (-1: the item has no such half)
             auto item_half = [&](const Item& x) -> int {
-                return x.valid ? __ldg(reinterpret_cast<const int*>(plan_halves) + 2 * x.qt + (warp >> 1)) : -1;
+                return x.valid ? __ldg(reinterpret_cast<const int*>(plan_halves) + 2 * x.qt + hsel) : -1;
             };
             auto item_row_base = [&](const Item& x, int half_row) -> int {
-                const int r = half_row + (lr & 63);
+                const int r = half_row + rih;
                 return (x.valid && x.n > 0 && half_row >= 0 && r < p.seq_len) ? __ldg(p.part_row_ptr + (r >> p.bm_shift)) : 0;
             };
             auto item_codes = [&](const Item& x) -> const uint2* {
-                return reinterpret_cast<const uint2*>(plan_codes + (static_cast<size_t>(x.qt) * p.max_tiles) * 32 + rg * 4);
+                return reinterpret_cast<const uint2*>(plan_codes + (static_cast<size_t>(x.qt) * p.max_steps) * 32 + rg * 4);
             };
             unsigned char* slab = o_smem + warp * A_OSTAGE_BYTES;       // this warp's 32 x 128 B output staging (1024-aligned)
-            // writes one fp16 output row (8 x 16 B) into the slab in the 128-byte-swizzled layout of the output tensor map,
-            // then one lane hands the slab to the TMA store; rows beyond the sequence end are clipped by the tensor map
+            // writes one fp16 output row (8 x 16 B) into the slab in the 128-byte-swizzled layout of the output tensor map
+            // (slab rows 0-15: half A, 16-31: half B), then one lane per half hands its 16 rows to the TMA store; rows beyond the
+            // sequence end are clipped by the tensor map
             auto store_rows = [&](const uint4 (&u)[8], const Item& x, int half_row) {
-                if (half_row < 0) return;                                // same in every lane of the warp
-                if (lane == 0) tma_store_wait_read();                    // the previous store has finished reading the slab
+                if ((lane & 15) == 0) tma_store_wait_read();             // this lane's previous store has finished reading the slab
                 __syncwarp();
 #pragma unroll
                 for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(slab + lane * 128 + ((c ^ (lane & 7)) << 4)) = u[c];
                 fence_proxy_async_smem();
                 __syncwarp();
-                if (lane == 0) {
-                    tma_tile_store(&map_o, slab, half_row + (warp & 1) * 32, x.head, x.batch, p.slot_s[3], p.slot_h[3], p.slot_b[3]);
+                if ((lane & 15) == 0 && half_row >= 0) {
+                    tma_tile_store(&map_o, slab + hsel * (A_OSTAGE_BYTES / 2), half_row + warp * 16, x.head, x.batch, p.slot_s[3], p.slot_h[3],
+                                   p.slot_b[3]);
                     tma_store_commit();
                 }
             };
@@ -586,7 +743,7 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             for (unsigned k = 0; item.valid; ++k) {
                 const Item cur_item = item;
                 const int part_base = part_base_next;
-                uint2 cw = cw_next;                              // codes of tile 0
+                uint2 cw = cw_next;                              // codes of step 0
                 const int half_row = half_next;
                 item = item2;
                 half_next = half2;
@@ -607,23 +764,29 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 float m_ref = -INFINITY, l_sum = 0.f;
 
                 for (int j = 0; j < n; ++j, ++g) {
-                    const int b = static_cast<int>(g % A_SBUF);
+                    const int b = sbuf;
+                    const uint32_t bphase = sphase;
+                    if (++sbuf == A_SBUF) { sbuf = 0; sphase ^= 1u; }
                     const uint2 cur = cw;
-                    if (j + 1 < n) cw = __ldg(my_codes + (j + 1) * 8);     // 32 codes = 64 B = 8 uint2 per tile
-                    // class of this warp's 32 x 64 part of the tile, put into the codes by the plan: the same value in every lane
+                    if (j + 1 < n) cw = __ldg(my_codes + (j + 1) * 8);     // 32 codes = 64 B = 8 uint2 per step
+                    // class of this warp's 32 x 64 part of the step, put into the codes by the plan: the same value in every lane
                     const unsigned warp_class = cur.y >> 30;
-                    const bool warp_absent = warp_class == 0u, warp_full = warp_class == 1u;
-                    mbar_wait(&bars[AB_S_FULL + b], (g / A_SBUF) & 1, wctx, AB_S_FULL + b);
+                    const bool warp_absent = warp_class == 0u, warp_fast = warp_class == 1u;
+                    // a thread whose 16-row group lists nothing of this step keeps its maximum and its sum: either its half has no
+                    // tile at this step (no product was issued for it: the scores it loads are stale and what it computes from
+                    // them is never used) or its scores were all set to -inf by the masking (P = 0)
+                    const bool present = (cur.x | (cur.y & 0x3FFFFFFFu)) != 0u;
+                    mbar_wait(&bars[AB_S_FULL + b], bphase, wctx, AB_S_FULL + b);
                     tc_fence_after();
                     uint32_t r0[32], r1[32];
                     if (warp_absent) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i) r0[i] = 0u;
                     } else {
-                        if (!warp_full)
+                        if (!warp_fast)
                             mask_scores_in_tmem(t_lane + A_COL_S + b * A_TKV, cur.x, cur.y, p.part_block_mask, part_base, p.bm_shift, p.bn,
-                                                (half_row + (lr & 63)) & (p.bm - 1),
-                                                static_cast<int>(plan_tiles[static_cast<size_t>(cur_item.qt) * p.max_tiles + j]) * A_TKV);
+                                                (half_row + rih) & (p.bm - 1),
+                                                static_cast<int>((__ldg(plan_steps + static_cast<size_t>(cur_item.qt) * p.max_steps + j) >> (16 * hsel)) & 0xFFFFu) * A_TKV);
                         tmem_ld32(t_lane + A_COL_S + b * A_TKV, r0);
                         tmem_ld32(t_lane + A_COL_S + b * A_TKV + 32, r1);
                         tc_wait_ld();
@@ -638,7 +801,7 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                         }
                         const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale;
                         // lazy rescale: move the reference maximum only when it would grow by more than the threshold
-                        const bool need = mx > m_ref + A_RESCALE_THRESHOLD || (m_ref == -INFINITY && mx > -INFINITY);
+                        const bool need = present && (mx > m_ref + A_RESCALE_THRESHOLD || (m_ref == -INFINITY && mx > -INFINITY));
                         if (__any_sync(0xffffffffu, need)) {
                             float alpha = 1.0f;
                             if (need) {
@@ -683,10 +846,10 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                         }
                         float sa0, sa1;
                         upk2(add2(sum_a, sum_b), sa0, sa1);
-                        l_sum += sa0 + sa1;
+                        if (present) l_sum += sa0 + sa1;
                     }
                     // P overlays the first 32 columns of the S buffer it was computed from; the QK^T that next writes this
-                    // buffer is issued after the PV product that reads P and the tensor core executes them in that order
+                    // buffer is issued after the PV products that read P and the tensor core executes them in that order
                     tmem_st32(t_lane + A_COL_S + b * A_TKV, r0);
                     tc_wait_st();
                     tc_fence_before();
@@ -706,21 +869,23 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bars[AB_O_FREE]);
                     {
-                        const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.0f;
+                        // a row that accumulated nothing (no listed key, or a half without any step: its O was never written) gives zeros
+                        const bool any = l_sum > 0.f;
+                        const float inv = any ? 1.0f / l_sum : 0.0f;
                         uint4 u[8];
 #pragma unroll
                         for (int c = 0; c < 8; ++c) {
                             const uint32_t* src = (c < 4) ? &o0[c * 8] : &o1[(c - 4) * 8];
-                            u[c].x = pack_half2(__uint_as_float(src[0]) * inv, __uint_as_float(src[1]) * inv);
-                            u[c].y = pack_half2(__uint_as_float(src[2]) * inv, __uint_as_float(src[3]) * inv);
-                            u[c].z = pack_half2(__uint_as_float(src[4]) * inv, __uint_as_float(src[5]) * inv);
-                            u[c].w = pack_half2(__uint_as_float(src[6]) * inv, __uint_as_float(src[7]) * inv);
+                            u[c].x = any ? pack_half2(__uint_as_float(src[0]) * inv, __uint_as_float(src[1]) * inv) : 0u;
+                            u[c].y = any ? pack_half2(__uint_as_float(src[2]) * inv, __uint_as_float(src[3]) * inv) : 0u;
+                            u[c].z = any ? pack_half2(__uint_as_float(src[4]) * inv, __uint_as_float(src[5]) * inv) : 0u;
+                            u[c].w = any ? pack_half2(__uint_as_float(src[6]) * inv, __uint_as_float(src[7]) * inv) : 0u;
                         }
                         store_rows(u, cur_item, half_row);
                     }
                 }
             }
-            if (lane == 0) tma_store_wait_all();             // every output store of this warp has been performed
+            if ((lane & 15) == 0) tma_store_wait_all();      // every output store of this warp has been performed
         }
     }
     tc_fence_before();
@@ -731,7 +896,7 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     }
 }
 
-constexpr size_t A_SMEM_BYTES = 1024 + 2 * A_Q_BYTES + static_cast<size_t>(A_KSLOTS + A_VSLOTS) * A_KV_BYTES + 4 * A_OSTAGE_BYTES + AB_COUNT * 8 + 16;
+constexpr size_t A_SMEM_BYTES = 1024 + A_QBUFS * A_QBUF_BYTES + static_cast<size_t>(A_KSLOTS + A_VSLOTS) * A_KV_BYTES + 4 * A_OSTAGE_BYTES + AB_COUNT * 8 + 16;
 
 // Sorts the three outer dimensions (row, head, batch) by stride so that the tensor map's strides ascend;
 // returns the coordinate slot of each logical dimension.
@@ -760,9 +925,9 @@ int log2_exact(int v) {
     return s;
 }
 
-// shared memory of the plan kernel: one 16-bit code per (row block of either half, column block)
+// shared memory of the plan kernel: one 16-bit code per (row block of either half, column block), then three lists of key tiles
 size_t plan_table_bytes(int seq_len, int block_m, int block_n) {
-    return static_cast<size_t>(2 * (block_m >= 64 ? 1 : 64 / block_m)) * (seq_len / block_n) * 2;
+    return static_cast<size_t>(2 * (block_m >= 64 ? 1 : 64 / block_m)) * (seq_len / block_n) * 2 + 3 * static_cast<size_t>((seq_len + A_TKV - 1) / A_TKV) * 2;
 }
 
 int check_blocks(int seq_len, int block_m, int block_n) {
@@ -865,7 +1030,7 @@ static int launch_block_attn(const void* q, const void* k, const void* v, void* 
     p.batch = batch; p.heads = heads; p.seq_len = seq_len; p.bm = block_m; p.bn = block_n;
     p.bm_shift = log2_exact(block_m); p.bn_shift = log2_exact(block_n);
     p.n_qtiles = (seq_len + A_TQ - 1) / A_TQ;
-    p.max_tiles = (seq_len + A_TKV - 1) / A_TKV;
+    p.max_steps = (seq_len + A_TKV - 1) / A_TKV;
     p.scale_log2 = softmax_scale * 1.4426950408889634f;
     p.status = status_dev;
     p.schedule = schedule;
@@ -873,9 +1038,11 @@ static int launch_block_attn(const void* q, const void* k, const void* v, void* 
     STOF_REQUIRE(items < (1ll << 31), "block_attn: batch * heads * query tiles beyond 2^31");
     p.total_items = static_cast<unsigned>(items);
     p.bh_total = static_cast<unsigned>(batch) * static_cast<unsigned>(heads);
-    CUtensorMap mq, mk, mv, mo;
-    if (int rc = make_qkv_map(&mo, out, batch, heads, seq_len, out_strides, 32, &p.slot_s[3], &p.slot_h[3], &p.slot_b[3])) return rc;
+    CUtensorMap mq, mq16, mk, mv, mo;
+    int unused_slot[3];
+    if (int rc = make_qkv_map(&mo, out, batch, heads, seq_len, out_strides, 16, &p.slot_s[3], &p.slot_h[3], &p.slot_b[3])) return rc;
     if (int rc = make_qkv_map(&mq, q, batch, heads, seq_len, q_strides, A_TQ / 2, &p.slot_s[0], &p.slot_h[0], &p.slot_b[0])) return rc;
+    if (int rc = make_qkv_map(&mq16, q, batch, heads, seq_len, q_strides, 16, &unused_slot[0], &unused_slot[1], &unused_slot[2])) return rc;
     if (int rc = make_qkv_map(&mk, k, batch, heads, seq_len, k_strides, A_TKV, &p.slot_s[1], &p.slot_h[1], &p.slot_b[1])) return rc;
     if (int rc = make_qkv_map(&mv, v, batch, heads, seq_len, v_strides, A_TKV, &p.slot_s[2], &p.slot_h[2], &p.slot_b[2])) return rc;
 
@@ -895,7 +1062,7 @@ static int launch_block_attn(const void* q, const void* k, const void* v, void* 
         STOF_REQUIRE((reinterpret_cast<uintptr_t>(schedule) & 3u) == 0, "block_attn: schedule must be 4-byte aligned");
         grid = schedule_blocks;
     }
-    block_attn_kernel<<<static_cast<unsigned>(grid), A_THREADS, A_SMEM_BYTES, stream>>>(mq, mk, mv, mo, p);
+    block_attn_kernel<<<static_cast<unsigned>(grid), A_THREADS, A_SMEM_BYTES, stream>>>(mq, mq16, mk, mv, mo, p);
     STOF_CUDA(cudaGetLastError());
     return STOF_OK;
 }

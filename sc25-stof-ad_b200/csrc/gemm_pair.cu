@@ -15,6 +15,7 @@
 // that neither frees shared or tensor memory its peer may still signal, read or write.
 #include "stof_host.h"
 #include "stof_ptx.cuh"
+#include "stof_epilogue.cuh"
 
 namespace stof {
 namespace {
@@ -32,23 +33,6 @@ constexpr size_t P_SMEM = 1024 + static_cast<size_t>(P_STAGES) * P_STAGE_BYTES +
 
 enum { PB_FULL = 0, PB_EMPTY = P_STAGES, PB_TFULL = 2 * P_STAGES, PB_TEMPTY = 2 * P_STAGES + 2, PB_COUNT = 2 * P_STAGES + 4 };
 
-__device__ __forceinline__ uint32_t cluster_rank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-// address of the same shared-memory location in block `rank` of the cluster
-__device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
-    return r;
-}
-__device__ __forceinline__ void remote_arrive(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
 __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int c0, int c1) {
     asm volatile(
         "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -75,41 +59,6 @@ __device__ __forceinline__ void tmem_relinquish_pair() {
 }
 __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-
-// erf-form GELU on a packed pair: x * Phi(x) with Phi(x) - 0.5 = x * g(x^2), g a degree-8 polynomial fitted on |x| <= 4.5
-// (|error of Phi| < 2.4e-5, of the GELU value < 1.1e-4, below half an fp16 step of any output above 0.1); x^2 is capped at 4.5^2
-// and 0.5 + x g saturates to [0, 1], so the tails are exactly 0 and x.  Ten packed FMAs / products and four scalar
-// instructions per pair, where an erf by the 7.1.28 rational form of Abramowitz & Stegun took about twice as many.
-__device__ __forceinline__ float2 gelu_erf2(float2 x2) {
-    float x0, x1, u0, u1;
-    upk2(x2, x0, x1);
-    upk2(mul2(x2, x2), u0, u1);
-    const float2 u = pk2(fminf(u0, 20.25f), fminf(u1, 20.25f));
-    float2 g = fma2(pk2(3.805775833e-11f, 3.805775833e-11f), u, pk2(-4.002384202e-09f, -4.002384202e-09f));
-    g = fma2(g, u, pk2(1.846188695e-07f, 1.846188695e-07f));
-    g = fma2(g, u, pk2(-4.959777016e-06f, -4.959777016e-06f));
-    g = fma2(g, u, pk2(8.727704699e-05f, 8.727704699e-05f));
-    g = fma2(g, u, pk2(-1.076741493e-03f, -1.076741493e-03f));
-    g = fma2(g, u, pk2(9.729498066e-03f, 9.729498066e-03f));
-    g = fma2(g, u, pk2(-6.624044478e-02f, -6.624044478e-02f));
-    g = fma2(g, u, pk2(3.988665044e-01f, 3.988665044e-01f));
-    float g0, g1;
-    upk2(g, g0, g1);
-    return mul2(x2, pk2(__saturatef(fmaf(x0, g0, 0.5f)), __saturatef(fmaf(x1, g1, 0.5f))));
-}
-// tanh-form GELU: 0.5 x (1 + tanh(u)) = x * sigmoid(2u), u = 0.79788456 (x + 0.044715 x^3)
-__device__ __forceinline__ float2 gelu_tanh2(float2 x2) {
-    const float2 xx = mul2(x2, x2);
-    const float2 inner = fma2(xx, pk2(0.044715f * 0.7978845608028654f, 0.044715f * 0.7978845608028654f),
-                                pk2(0.7978845608028654f, 0.7978845608028654f));
-    float u0, u1, x0, x1;
-    upk2(mul2(inner, x2), u0, u1);
-    upk2(x2, x0, x1);
-    // sigmoid(2u) = 1 / (1 + 2^(-2u log2 e))
-    const float s0 = __fdividef(1.0f, 1.0f + fast_exp2(-2.8853900817779268f * u0));
-    const float s1 = __fdividef(1.0f, 1.0f + fast_exp2(-2.8853900817779268f * u1));
-    return pk2(x0 * s0, x1 * s1);
 }
 
 template <int EPI>

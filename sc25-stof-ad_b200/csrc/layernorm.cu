@@ -57,7 +57,7 @@ template <int NCHUNK>
 __global__ void __launch_bounds__(LN_WARPS * 32)
 layernorm_kernel(const __half* x, long long ldx, const __half* __restrict__ bias, const __half* __restrict__ residual,
                  long long ldr, const __half* __restrict__ gamma, const __half* __restrict__ beta, float eps, __half* y,
-                 long long ldy, int rows, int hidden) {
+                 long long ldy, int rows, int hidden, int* status) {
     extern __shared__ __align__(128) unsigned char ln_smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int warps_total = gridDim.x * LN_WARPS;
@@ -116,8 +116,12 @@ layernorm_kernel(const __half* x, long long ldx, const __half* __restrict__ bias
         for (int it = 0; row < rows; row += warps_total, ++it) {
             const int s = it % LN_STAGES;
             const uint32_t parity = static_cast<uint32_t>((it / LN_STAGES) & 1);
-            // completes with the copy (no partner thread involved); bounded all the same: ~1.6 s of suspended polls
-            for (int spin = 0; !mbar_try_wait(&bars[s], parity) && spin < (1 << 14); ++spin) { }
+            // completes with the copy (no partner thread involved); bounded all the same by a cycle budget: a warp whose copy
+            // never lands reports it and leaves its remaining rows unwritten instead of normalising stale shared memory
+            if (!__all_sync(0xffffffffu, mbar_wait_budget(&bars[s], parity))) {
+                if (lane == 0 && status) atomicCAS(status, 0, (s << 8) | STATUS_WAIT_TIMEOUT);
+                break;
+            }
             const unsigned char* src = ring + static_cast<size_t>(s) * slot_bytes;
             float2 v[NCHUNK][4];
             float2 sum2 = make_float2(0.f, 0.f);
@@ -248,7 +252,7 @@ using namespace stof;
 
 extern "C" int stof_bias_residual_layernorm(const void* x, long long ldx, const void* bias, const void* residual, long long ldr,
                                             const void* gamma, const void* beta, float eps, void* y, long long ldy, int rows, int hidden,
-                                            void* stream_) {
+                                            int* status_dev, void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     STOF_REQUIRE(x && y, "layernorm: null x or y");
     STOF_REQUIRE(rows >= 0 && hidden > 0, "layernorm: bad shape (%d, %d)", rows, hidden);
@@ -281,7 +285,7 @@ extern "C" int stof_bias_residual_layernorm(const void* x, long long ldx, const 
         if (per_sm > LN_BLOCKS_PER_SM) per_sm = LN_BLOCKS_PER_SM;                                                                   \
         int blocks = (rows + LN_WARPS - 1) / LN_WARPS;                                                                              \
         if (blocks > sm_count() * per_sm) blocks = sm_count() * per_sm;                                                             \
-        layernorm_kernel<N><<<dim3(blocks), block, ring_smem, stream>>>(xp, ldx, bp, rp, ldr, gp, tp, eps, yp, ldy, rows, hidden);  \
+        layernorm_kernel<N><<<dim3(blocks), block, ring_smem, stream>>>(xp, ldx, bp, rp, ldr, gp, tp, eps, yp, ldy, rows, hidden, status_dev);   \
     } while (0)
     if (hidden <= 256) STOF_LN_LAUNCH(1);
     else if (hidden <= 512) STOF_LN_LAUNCH(2);

@@ -342,7 +342,9 @@ fill_bounded_kernel(const void* __restrict__ mask, int seq_len, int bm, int bn, 
 
 // Device address of g_static_scratch on the current device.  In host code the array's name is only a
 // host-side handle, never a pointer a kernel may use, so the address is asked from the runtime once per
-// device (with that device current) and cached.
+// device (with that device current) and cached.  The query may be what makes the runtime load the module (and
+// with it the array) onto the device; the cached address dies with the device's primary context, so a
+// cudaDeviceReset() on that device leaves it stale.
 int static_scratch_address(unsigned char** out) {
     static std::mutex mu;
     static unsigned char* addr[64] = {};

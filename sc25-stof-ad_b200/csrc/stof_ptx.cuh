@@ -92,6 +92,65 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, const 
     }
 }
 
+// The same bounded wait without a CTA-wide abort flag, for waits nobody else can satisfy late (a thread's own bulk
+// copy): false when the cycle budget ran out.
+__device__ __forceinline__ bool mbar_wait_budget(uint64_t* bar, uint32_t parity, long long budget_cycles = WAIT_BUDGET_CYCLES) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity))
+        if (clock64() - t0 > budget_cycles) return false;
+    return true;
+}
+
+// ---------------------------------------------------------------------------------
+// Thread-block clusters: rank, mapped shared-memory addresses, remote barrier arrives
+// ---------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// address of the same shared-memory location in block `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void remote_arrive(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// The bounded wait with cluster-scope acquire: what the arriving threads of OTHER blocks of the cluster wrote into this
+// block's shared memory before their (release.cluster) arrives is visible afterwards.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred P;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(MBAR_SUSPEND_HINT_NS)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void mbar_wait_cluster(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, int barrier_id) {
+    if (mbar_try_wait_cluster(bar, parity)) return;
+    const long long t0 = clock64();
+    int spins = 0;
+    while (!mbar_try_wait_cluster(bar, parity)) {
+        if ((++spins & 3) == 0) {
+            if (*ctx.abort_smem) return;
+            if (clock64() - t0 > WAIT_BUDGET_CYCLES) {
+                *ctx.abort_smem = 1;
+                if (ctx.status_gmem) atomicCAS(ctx.status_gmem, 0, (barrier_id << 8) | STATUS_WAIT_TIMEOUT);
+                return;
+            }
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------
 // TMA tile loads (per-CTA, own-GPU memory only, completion on an mbarrier)
 // ---------------------------------------------------------------------------------

@@ -12,7 +12,7 @@ STOF_DTYPE_F16, STOF_DTYPE_F32 = 0, 1
 EPI_BIAS, EPI_BIAS_GELU_ERF, EPI_BIAS_GELU_TANH, EPI_BIAS_RESIDUAL, EPI_BIAS_RELU = 0, 1, 2, 3, 4
 
 EXPORTS = ("stof_version", "stof_last_error", "stof_mask_workspace_bytes", "stof_mask_classify", "stof_mask_fill", "stof_mask_compact_static",
-           "stof_block_attn_plan_bytes", "stof_block_attn_plan", "stof_block_attn_plan_paired", "stof_block_attn", "stof_block_attn_scheduled", "stof_gemm_bias_act", "stof_bias_residual_layernorm")
+           "stof_block_attn_plan_bytes", "stof_block_attn_plan", "stof_block_attn_plan_paired", "stof_block_attn", "stof_block_attn_scheduled", "stof_gemm_bias_act", "stof_gemm_bias_residual_layernorm", "stof_bias_residual_layernorm")
 
 
 class StofError(RuntimeError):
@@ -62,8 +62,10 @@ def lib() -> ctypes.CDLL:
                                             vp, vp, vp, i32, i32, i32, f32, vp, i32, vp, vp]
     L.stof_gemm_bias_act.restype = i32
     L.stof_gemm_bias_act.argtypes = [vp, i64, vp, i64, vp, vp, i64, vp, i64, i32, i32, i32, i32, vp, vp]
+    L.stof_gemm_bias_residual_layernorm.restype = i32
+    L.stof_gemm_bias_residual_layernorm.argtypes = [vp, i64, vp, i64, vp, vp, i64, vp, vp, f32, vp, i64, i32, i32, i32, vp, vp]
     L.stof_bias_residual_layernorm.restype = i32
-    L.stof_bias_residual_layernorm.argtypes = [vp, i64, vp, vp, i64, vp, vp, f32, vp, i64, i32, i32, vp]
+    L.stof_bias_residual_layernorm.argtypes = [vp, i64, vp, vp, i64, vp, vp, f32, vp, i64, i32, i32, vp, vp]
     _lib = L
     return L
 

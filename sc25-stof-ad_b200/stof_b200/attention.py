@@ -13,17 +13,32 @@ _PLAN_CACHE = OrderedDict()
 _PLAN_CACHE_MAX = 16
 
 
-_PAIR_MIN_GAIN = 0.08                # pair the halves only when that spares at least this share of the tile steps
+_INDEX_GENERATION = {}               # data pointer of an index tensor -> number of in-place rewrites announced by its owner
+
+
+def index_rewritten(*tensors):
+    """Tells the plan cache that these index tensors were rewritten in place by something torch does not see (a C-ABI
+    call such as `stof_mask_compact_static`): their version counters did not move, so the cache key carries a
+    generation number per storage that this call advances.  Plans and schedules made from the old contents are then
+    never found again (they age out of the caches)."""
+    for t in tensors:
+        if t is not None:
+            _INDEX_GENERATION[t.data_ptr()] = _INDEX_GENERATION.get(t.data_ptr(), 0) + 1
+
+
+_PAIR_MIN_GAIN = 0.06                # re-pair the halves only when that lowers the estimated cost by at least this share
+_PAIR_LOAD_WEIGHT = 0.25             # cost of loading one K/V tile pair, in units of one step of the softmax warps
 _HOT_PLANS = set()                   # data pointers of plans that were used more than once (see attention_schedule)
 
 
 def pair_halves(full_row_ptr, full_col_idx, part_row_ptr, part_col_idx, seq_len: int, block_m: int, block_n: int):
-    """Chooses, for `stof_block_attn_plan_paired`, which two 64-row halves of the sequence form each 128-row query tile.
-    A tile costs one step per 64-wide key tile that either of its halves lists, so halves with similar lists belong
-    together (rows r and r + 2 of a dilated mask, say).  Greedy matching: the halves with the longest lists choose first
-    and take the free half with which the union is smallest (ties: the neighbour 2t / 2t + 1, then the nearest); then
-    pairs of tiles exchange partners while that shortens the total.
-    Takes the index as host sequences or CPU tensors.  Returns (pairs, steps_default, steps_paired); pairs is a list of
+    """Chooses, for `stof_block_attn_plan_paired`, which two 64-row halves of the sequence form each work item.
+    The two halves of an item walk their own key-tile lists side by side, so an item takes max(len A, len B) steps and
+    loads |A union B| tiles: halves with equally long lists belong together, and among those the ones whose lists agree.
+    Greedy matching on cost = steps + `_PAIR_LOAD_WEIGHT` * loads: the halves with the longest lists choose first and
+    take the free half that is cheapest to pair with (ties: the neighbour 2t / 2t + 1, then the nearest); then pairs of
+    items exchange partners while that lowers the total.
+    Takes the index as host sequences or CPU tensors.  Returns (pairs, cost_default, cost_paired); pairs is a list of
     ceil(seq_len / 128) (half, half-or--1) tuples, or None when pairing gains less than `_PAIR_MIN_GAIN`.  Pure host code."""
     import numpy as np
     frp, fci, prp, pci = (np.asarray(t, dtype=np.int64) for t in (full_row_ptr, full_col_idx, part_row_ptr, part_col_idx))
@@ -42,7 +57,8 @@ def pair_halves(full_row_ptr, full_col_idx, part_row_ptr, part_col_idx, seq_len:
     size = lists.sum(axis=1).astype(np.int64)
     both = lists.astype(np.int64) @ lists.astype(np.int64).T
     union = size[:, None] + size[None, :] - both
-    steps_default = int(sum(union[2 * t, 2 * t + 1] for t in range(n // 2)))
+    cost = np.maximum(size[:, None], size[None, :]) + _PAIR_LOAD_WEIGHT * union
+    cost_default = float(sum(cost[2 * t, 2 * t + 1] for t in range(n // 2)))
     free = np.ones(n, dtype=bool)
     idx = np.arange(n)
     pairs = []
@@ -50,41 +66,41 @@ def pair_halves(full_row_ptr, full_col_idx, part_row_ptr, part_col_idx, seq_len:
         if not free[a]:
             continue
         free[a] = False
-        # smallest union first; among equals the default neighbour, then the nearest half
-        key = union[a] * (4 * n) + np.where(idx == (a ^ 1), 0, 2 * np.abs(idx - a) + 1)
-        b = int(np.argmin(np.where(free, key, np.iinfo(np.int64).max)))
+        # cheapest partner first; among equals the default neighbour, then the nearest half
+        key = cost[a] * (4 * n) + np.where(idx == (a ^ 1), 0, 2 * np.abs(idx - a) + 1)
+        b = int(np.argmin(np.where(free, key, np.inf)))
         free[b] = False
         pairs.append([int(a), b])
-    # pairwise exchange: swap partners between two tiles while that shortens the total
-    union = union.tolist()                               # plain lists: the loop below is scalar work
+    # pairwise exchange: swap partners between two items while that lowers the total
+    cost = cost.tolist()                                 # plain lists: the loop below is scalar work
     improved, rounds = True, 0
     while improved and rounds < 16:
         improved, rounds = False, rounds + 1
         for i in range(len(pairs)):
             for j in range(i + 1, len(pairs)):
                 (a, b), (c, d) = pairs[i], pairs[j]
-                now, swap1, swap2 = union[a][b] + union[c][d], union[a][c] + union[b][d], union[a][d] + union[b][c]
-                if swap1 < now and swap1 <= swap2:
+                now, swap1, swap2 = cost[a][b] + cost[c][d], cost[a][c] + cost[b][d], cost[a][d] + cost[b][c]
+                if swap1 < now - 1e-9 and swap1 <= swap2:
                     pairs[i], pairs[j], improved = [a, c], [b, d], True
-                elif swap2 < now:
+                elif swap2 < now - 1e-9:
                     pairs[i], pairs[j], improved = [a, d], [b, c], True
-    steps_paired = int(sum(union[a][b] for a, b in pairs))
-    if steps_default == 0 or steps_paired > (1.0 - _PAIR_MIN_GAIN) * steps_default:
-        return None, steps_default, steps_paired
+    cost_paired = float(sum(cost[a][b] for a, b in pairs))
+    if cost_default == 0 or cost_paired > (1.0 - _PAIR_MIN_GAIN) * cost_default:
+        return None, cost_default, cost_paired
     out = []
     for a, b in pairs:
         a, b = (a, b) if a < b else (b, a)
         out.append((a, b if b < n_half else -1))
     out.sort()
-    return out, steps_default, steps_paired
+    return out, cost_default, cost_paired
 
 
 def plan_halves(plan, seq_len: int):
-    """View of a plan's half table: int32 (query tiles, 2), the first sequence row of the two 64-row halves of each
-    128-row query tile (-1: no second half)."""
+    """View of a plan's half table: int32 (items, 2), the first sequence row of the two 64-row halves of each work item
+    (-1: no second half)."""
     nqt, maxt = (seq_len + 127) // 128, (seq_len + 63) // 64
     a16 = lambda x: (x + 15) & ~15
-    off = 32 + a16(4 * nqt) + a16(8 * nqt) + a16(2 * nqt * maxt) + 64 * nqt * maxt
+    off = 32 + a16(4 * nqt) + a16(8 * nqt) + a16(4 * nqt * maxt) + 64 * nqt * maxt
     return plan[off:off + 8 * nqt].view(torch.int32).view(nqt, 2)
 
 
@@ -114,7 +130,8 @@ def attention_plan(full_row_ptr, full_col_idx, part_row_ptr, part_col_idx, seq_l
     once and re-plans with `pair_halves` when that spares tile steps (an index used once is not worth the host read);
     "eager" does so at once, "off" never."""
     tensors = (full_row_ptr, full_col_idx, part_row_ptr, part_col_idx)
-    key = tuple((t.data_ptr(), t._version, t.numel()) for t in tensors) + (seq_len, block_m, block_n, str(full_row_ptr.device))
+    key = tuple((t.data_ptr(), t._version, t.numel(), _INDEX_GENERATION.get(t.data_ptr(), 0)) for t in tensors) + \
+        (seq_len, block_m, block_n, str(full_row_ptr.device))
     hit = _PLAN_CACHE.get(key)
     if hit is not None:
         _PLAN_CACHE.move_to_end(key)

@@ -10,7 +10,7 @@ import torch
 
 from . import _lib
 from .attention import block_attention
-from .fused import bias_residual_layernorm, gemm_bias, gemm_bias_act, gemm_bias_residual
+from .fused import bias_residual_layernorm, gemm_bias, gemm_bias_act, gemm_bias_residual, gemm_bias_residual_layernorm
 from .masks import get_sparse_storage
 
 
@@ -37,14 +37,18 @@ class EncoderWeights:
 
 
 class BertEncoder:
-    """Forward-only encoder.  Per layer six kernel launches:
+    """Forward-only encoder.  Per layer five kernel launches:
     QKV GEMM+bias -> block-masked attention reading Q/K/V straight out of the fused QKV activation and
-    writing merged heads -> out-proj GEMM+bias+residual -> LayerNorm -> FFN1 GEMM+bias+GELU ->
-    FFN2 GEMM+bias+residual -> LayerNorm.  The block index is built once per mask."""
+    writing merged heads -> out-proj GEMM+bias+residual+LayerNorm -> FFN1 GEMM+bias+GELU ->
+    FFN2 GEMM+bias+residual+LayerNorm (seven with `fuse_layernorm=False`: the two LayerNorms as kernels of their
+    own after GEMMs with the bias + residual epilogue).  The block index is built once per mask.
+    The tensor `forward` returns is one of the encoder's own buffers: it holds the result until the next forward
+    pass (or graph replay) of this encoder; clone it to keep it longer."""
 
     def __init__(self, layers: List[EncoderWeights], head_num: int, eps: float = 1e-12, gelu: str = "erf",
-                 block_m: int = 64, block_n: int = 64):
+                 block_m: int = 64, block_n: int = 64, fuse_layernorm: bool = True):
         """`gelu` names the feed-forward activation: "erf" (BERT), "tanh" (GPT-2 `new_gelu`) or "relu" (T5)."""
+        self.fuse_layernorm = bool(fuse_layernorm)
         if gelu not in ("erf", "tanh", "relu"):
             raise _lib.StofError(f"encoder: unknown activation {gelu!r}")
         self.layers = layers
@@ -83,7 +87,10 @@ class BertEncoder:
         ctx = self._buf("ctx", (B, S, hid), dev)
         ffn = self.layers[0].W1.shape[1]
         inter = self._buf("inter", (B, S, ffn), dev)
+        # three hidden-state buffers in rotation: while a GEMM writes one, the previous one is still its residual input and the
+        # one before that may be the caller's view of the last result
         y_bufs = [self._buf("y0", (B, S, hid), dev), self._buf("y1", (B, S, hid), dev), self._buf("y2", (B, S, hid), dev)]
+        assert len(y_bufs) >= 3
         yi = 0
         for w in self.layers:
             gemm_bias(x, w.Wqkv, w.bqkv, out=qkv)
@@ -94,12 +101,18 @@ class BertEncoder:
             o = ctx.view(B, S, H, D).permute(0, 2, 1, 3)
             block_attention(q, k, v, o, frp, fci, prp, pci, pbm, lrp, lci, self.block_m, self.block_n)
             y = y_bufs[yi]; yi = (yi + 1) % 3
-            gemm_bias_residual(ctx, w.Wo, w.bo, x, out=y)
-            bias_residual_layernorm(y, None, None, w.g1, w.b1, self.eps, out=y)
+            if self.fuse_layernorm:
+                gemm_bias_residual_layernorm(ctx, w.Wo, w.bo, x, w.g1, w.b1, self.eps, out=y)
+            else:
+                gemm_bias_residual(ctx, w.Wo, w.bo, x, out=y)
+                bias_residual_layernorm(y, None, None, w.g1, w.b1, self.eps, out=y)
             gemm_bias_act(y, w.W1, w.bi1, self.gelu, out=inter)
             z = y_bufs[yi]; yi = (yi + 1) % 3
-            gemm_bias_residual(inter, w.W2, w.bi2, y, out=z)
-            bias_residual_layernorm(z, None, None, w.g2, w.b2, self.eps, out=z)
+            if self.fuse_layernorm:
+                gemm_bias_residual_layernorm(inter, w.W2, w.bi2, y, w.g2, w.b2, self.eps, out=z)
+            else:
+                gemm_bias_residual(inter, w.W2, w.bi2, y, out=z)
+                bias_residual_layernorm(z, None, None, w.g2, w.b2, self.eps, out=z)
             x = z
         return x
 
@@ -173,7 +186,8 @@ class T5DecoderWeights:
 class T5Decoder(BertEncoder):
     """Decoder layers of the reference's T5 loop (src/benchmk_end2end.py:230-316): masked self-attention, a second
     attention sublayer on the decoder state, and the ReLU feed-forward, each followed by residual + LayerNorm.  Per layer
-    ten kernel launches (3 QKV/out-proj GEMM pairs and FFN GEMMs with fused epilogues, 2 attentions, 3 LayerNorms)."""
+    seven kernel launches (two QKV GEMMs, two attentions, two out-projections and the second FFN GEMM with the residual + LayerNorm
+    epilogue, the first FFN GEMM with ReLU)."""
 
     def __init__(self, layers: List[T5DecoderWeights], head_num: int, eps: float = 1e-5, block_m: int = 64, block_n: int = 64):
         super().__init__(layers, head_num, eps, "relu", block_m, block_n)
@@ -197,8 +211,7 @@ class T5Decoder(BertEncoder):
             q5 = qkv.view(B, S, 3, H, D)
             q, k, v = (q5[:, :, i].permute(0, 2, 1, 3) for i in range(3))
             block_attention(q, k, v, ctx.view(B, S, H, D).permute(0, 2, 1, 3), frp, fci, prp, pci, pbm, lrp, lci, self.block_m, self.block_n)
-            gemm_bias_residual(ctx, Wo, bo, x, out=out)
-            bias_residual_layernorm(out, None, None, g, b, self.eps, out=out)
+            gemm_bias_residual_layernorm(ctx, Wo, bo, x, g, b, self.eps, out=out)
             return out
 
         x = hidden
@@ -207,8 +220,7 @@ class T5Decoder(BertEncoder):
             y2 = attention_sublayer(y, w.Wqkv_c, w.bqkv_c, w.Wo_c, w.bo_c, w.g_c, w.b_c, ys[yi]); yi = (yi + 1) % 4
             gemm_bias_act(y2, w.W1, w.bi1, "relu", out=inter)
             z = ys[yi]; yi = (yi + 1) % 4
-            gemm_bias_residual(inter, w.W2, w.bi2, y2, out=z)
-            bias_residual_layernorm(z, None, None, w.g2, w.b2, self.eps, out=z)
+            gemm_bias_residual_layernorm(inter, w.W2, w.bi2, y2, w.g2, w.b2, self.eps, out=z)
             x = z
         return x
 

@@ -50,6 +50,7 @@ def get_sparse_storage(Mask: torch.Tensor, block_size_m: int, block_size_n: int)
                                         _lib.ptr(row_ptrs[2]), _lib.ptr(counts), _lib.ptr(ws), ws_bytes, stream),
                    "stof_mask_classify")
         n_full, n_part, n_load, nnz_elems = counts.tolist()          # the one host read: output sizes depend on the data
+        _lib.check_status(dev, "a kernel launched before this get_sparse_storage")   # the stream is drained here anyway
         full_col = torch.empty(n_full, dtype=torch.int32, device=dev)
         part_col = torch.empty(n_part, dtype=torch.int32, device=dev)
         load_col = torch.empty(n_load, dtype=torch.int32, device=dev)
@@ -104,6 +105,9 @@ class SparseStorageRefresher:
                                             _lib.ptr(self._tiles), self._tile_cap if self._sizes[1] else 0,
                                             _lib.ptr(self._counts), _lib.current_stream_ptr(m.device))
         _lib.check(rc, "stof_mask_compact_static")
+        # the index was rewritten behind torch's back: plans cached for the old contents must not be found again
+        from .attention import index_rewritten
+        index_rewritten(self._row_ptrs[0], self._row_ptrs[1], self._row_ptrs[2], self._cols[0], self._cols[1], self._cols[2], self._tiles)
         return self.out
 
     def check(self):

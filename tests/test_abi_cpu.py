@@ -66,7 +66,7 @@ def test_argument_validation_needs_no_gpu(built_lib):
     assert rc == -3 and b"workspace" in L.stof_last_error()
     rc = L.stof_gemm_bias_act(one, 60, one, 64, None, None, 0, one, 64, 8, 64, 60, 0, None, None)
     assert rc == -1
-    rc = L.stof_bias_residual_layernorm(one, 16384, None, None, 0, None, None, 1e-5, one, 16384, 4, 16384, None)
+    rc = L.stof_bias_residual_layernorm(one, 16384, None, None, 0, None, None, 1e-5, one, 16384, 4, 16384, None, None)
     assert rc == -4 and b"8192" in L.stof_last_error()
     assert L.stof_mask_workspace_bytes(4096, 64, 64) == 16 + 64 * 64
 
@@ -182,9 +182,10 @@ def test_util_helpers_of_the_reference_scripts(tmp_path):
 
 
 def test_pair_halves_host_logic():
-    """`pair_halves` on block indices given as plain lists: a dilated window pairs halves r and r + 2 and spares tile
-    steps, every half lands in exactly one tile (an odd count leaves one alone), and a plain sliding window, whose
-    neighbours already agree, is left to the default tiling."""
+    """`pair_halves` on block indices given as plain lists: a dilated window pairs halves r and r + 2 (their key-tile lists
+    agree: fewer loads), rows with long and short lists in turn are paired long with long (fewer steps), every half lands
+    in exactly one item (an odd count leaves one alone), and a plain sliding window, whose neighbours already agree, is
+    left to the default pairing."""
     import numpy as np
     from stof_b200.attention import pair_halves
 
@@ -201,7 +202,8 @@ def test_pair_halves_host_logic():
         dil = (np.abs(d) <= 4) & (d % 2 == 0)
         ptr, col = index(dil)
         pairs, before, after = pair_halves(ptr, col, [0] * (nb + 1), [], nb * 64, 64, 64)
-        assert pairs is not None and after < 0.75 * before
+        assert pairs is not None and after < 0.9 * before
+        assert sum(1 for p in pairs if p[1] >= 0 and (p[1] - p[0]) % 2 == 0) >= len(pairs) - 3      # r with r + 2, but for the ends
         flat = [h for p in pairs for h in p if h >= 0]
         assert sorted(flat) == list(range(nb)) and len(pairs) == (nb + 1) // 2
         assert sum(1 for p in pairs if p[1] < 0) == nb % 2
@@ -213,6 +215,15 @@ def test_pair_halves_host_logic():
         slide = np.abs(d) <= 1
         ptr, col = index(slide)
         assert pair_halves(ptr, col, [0] * (nb + 1), [], nb * 64, 64, 64)[0] is None
+    # even rows list eight tiles, odd rows two: an item takes as many steps as its longer half, so like goes with like
+    nb = 32
+    uneven = np.zeros((nb, nb), bool)
+    for r in range(nb):
+        uneven[r, [(r + 3 * c) % nb for c in range(8 if r % 2 == 0 else 2)]] = True
+    ptr, col = index(uneven)
+    pairs, before, after = pair_halves(ptr, col, [0] * (nb + 1), [], nb * 64, 64, 64)
+    assert pairs is not None and after < 0.75 * before
+    assert all(a % 2 == b % 2 for a, b in pairs)
 
 
 def test_operator_selector_host_logic():

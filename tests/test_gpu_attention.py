@@ -134,9 +134,9 @@ def test_strided_qkv_views_and_merged_head_output():
     assert _err(oa.merge_heads(want), ctx.float().cpu()) <= TOL
 
 
-@pytest.mark.parametrize("name", ["cfg2_bigbird_S2048_seed1", "cfg3_longdil_S4096"])
+@pytest.mark.parametrize("name", ["cfg2_bigbird_S2048_seed1", "cfg3_longdil_S4096", "cfg5_bigbird_S4096_seed4"])
 def test_benchmark_configurations_at_full_sequence_length(name):
-    """Full sequence length and mask of the benchmark configurations on a slice of batch x heads that the
+    """Full sequence length and mask of the benchmark configurations (the two attention ones and the encoder's) on a slice of batch x heads that the
     dense CPU oracle finishes in seconds; plus a whole-tensor property: heads with equal inputs give equal
     outputs wherever they sit in the batch."""
     _, S, _, _ = om.RECIPES[name]
@@ -190,7 +190,8 @@ def test_rowwise_operators_match_their_oracles():
     rmd = rm.cuda()
     first = rowwise_attn_mask_op(qd, kd, vd, False, rmd)
     entries = len(rw._INDEX_CACHE)
-    assert torch.equal(rowwise_attn_mask_op(qd, kd, vd, False, rmd), first) and len(rw._INDEX_CACHE) == entries
+    again = rowwise_attn_mask_op(qd, kd, vd, False, rmd)           # the second use of an index may re-pair its halves: same values up to rounding
+    assert _err(again.float().cpu(), first.float().cpu()) <= 1e-3 and len(rw._INDEX_CACHE) == entries
     rmd[:, S // 2:] = 0
     rmd += torch.eye(S, dtype=torch.float16, device="cuda")
     rmd.clamp_(max=1)
@@ -375,3 +376,65 @@ def test_block_size_selection_and_every_granularity_agree():
     for blk in (16, 32, 64, 128):
         got = _run_op(q, k, v, _index(band, blk, blk), blk, blk)
         assert _err(got, want) <= TOL, blk
+
+
+@pytest.mark.gpu
+def test_halves_with_uneven_lists_are_paired_by_length():
+    """Row blocks that list eight and two key tiles in turn: an item takes as many steps as its longer half, so at the
+    second use of the index the host pairs long with long.  Both plans agree with the oracle; the shorter half of an
+    unevenly paired item sits out the last steps (first use), and every row is still written exactly once."""
+    import stof_b200
+    from stof_b200 import _lib, attention as A
+    dev = torch.device("cuda:0")
+    nb = 12
+    S = nb * 64
+    blocks = np.zeros((nb, nb), np.float32)
+    for r in range(nb):
+        blocks[r, [(r + 3 * c) % nb for c in range(8 if r % 2 == 0 else 2)]] = 1
+    blocks[5, :] = 0                                                       # and one half without any key at all
+    mask = om.expand_block_mask(blocks)
+    B, H = 2, 2
+    q, k, v = _qkv(B, H, S, seed=13)
+    qd, kd, vd = q.to(dev), k.to(dev), v.to(dev)
+    idx = _index(mask, 64, 64)
+    want = oa.block_attention_from_index(q, k, v, om.get_sparse_storage(mask, 64, 64), 64, 64)
+    first = stof_b200.block_attention(qd, kd, vd, torch.full_like(qd, 7.0), *idx, 64, 64)
+    default_halves = A.plan_halves(A.attention_plan(*idx[:4], S, 64, 64, pairing="off"), S).cpu().clone()
+    second = stof_b200.block_attention(qd, kd, vd, torch.full_like(qd, 7.0), *idx, 64, 64)
+    torch.cuda.synchronize()
+    _lib.check_status(dev, "uneven halves")
+    halves = A.plan_halves(A.attention_plan(*idx[:4], S, 64, 64, pairing="off"), S).cpu()
+    assert not torch.equal(halves, default_halves)
+    assert sorted(halves.flatten().tolist()) == list(range(0, S, 64))
+    assert all((a // 64) % 2 == (b // 64) % 2 for a, b in halves.tolist())
+    assert torch.all(first[:, :, 5 * 64:6 * 64] == 0) and torch.all(second[:, :, 5 * 64:6 * 64] == 0)
+    assert _err(first.float().cpu(), want) <= TOL
+    assert _err(second.float().cpu(), want) <= TOL
+
+
+@pytest.mark.gpu
+def test_attention_follows_an_index_refreshed_in_place():
+    """`SparseStorageRefresher` rewrites its index buffers in place through the C ABI (torch's version counters do not
+    move).  After the mask changed to another one with the same block counts, attention on the refreshed index must use
+    the new mask, not a plan cached for the old contents of the same buffers."""
+    import stof_b200
+    dev = torch.device("cuda:0")
+    S, B, H = 512, 1, 2
+    nb = S // 64
+    i = np.arange(nb)
+    first_blocks = (((i[None, :] - i[:, None]) % nb) < 3).astype(np.float32)      # three tiles to the right (cyclic)
+    second_blocks = (((i[:, None] - i[None, :]) % nb) < 3).astype(np.float32)     # three tiles to the left: same counts
+    mask_dev = torch.from_numpy(om.expand_block_mask(first_blocks)).to(dev)
+    q, k, v = _qkv(B, H, S, seed=17)
+    qd, kd, vd = q.to(dev), k.to(dev), v.to(dev)
+    refresher = stof_b200.SparseStorageRefresher(mask_dev, 64, 64)
+    for blocks in (first_blocks, second_blocks, first_blocks):
+        mask_np = om.expand_block_mask(blocks)
+        mask_dev.copy_(torch.from_numpy(mask_np))
+        idx = refresher.refresh()[1:]
+        for _ in range(2):                                                  # the second use may re-plan: same answer
+            got = stof_b200.block_attention(qd, kd, vd, torch.empty_like(qd), *idx, 64, 64)
+            torch.cuda.synchronize()
+            want = oa.masked_attention_fp32(q, k, v, torch.from_numpy(mask_np.astype(np.float32)))
+            assert _err(got.float().cpu(), want) <= TOL
+    refresher.check()

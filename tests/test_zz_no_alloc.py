@@ -34,6 +34,20 @@ def _static_call(mask_t, bm, bn, col_cap, part_cap):
     return row_ptrs, cols, tiles, counts.tolist()
 
 
+def _check_against_oracle(mask_np, bm, bn, row_ptrs, cols, tiles, counts):
+    """The same buffers against the CPU restatement of the reference's get_sparse_storage, bit for bit."""
+    st = om.get_sparse_storage(mask_np, bm, bn)
+    n_full, n_part, n_load, nnz_elems = counts
+    assert (n_full, n_part, n_load) == (st.full_col_idx.size, st.part_col_idx.size, st.load_col_idx.size)
+    assert nnz_elems == int(np.count_nonzero(mask_np))
+    for i, want in enumerate((st.full_row_ptr, st.part_row_ptr, st.load_row_ptr)):
+        assert np.array_equal(row_ptrs[i].cpu().numpy(), want)
+    for i, (n, want) in enumerate(((n_full, st.full_col_idx), (n_part, st.part_col_idx), (n_load, st.load_col_idx))):
+        assert np.array_equal(cols[i, :n].cpu().numpy(), want)
+    if n_part:
+        assert np.array_equal(tiles[:n_part].cpu().numpy().view(np.uint16), st.part_block_mask.view(np.uint16))
+
+
 def _check_against_two_phase(mask_np, bm, bn):
     import stof_b200
     mask_t = torch.from_numpy(mask_np).cuda()
@@ -48,6 +62,7 @@ def _check_against_two_phase(mask_np, bm, bn):
     if n_part:
         assert torch.equal(tiles[:n_part].view(torch.int16), pbm.view(torch.int16))           # bit-exact, like the index
     assert torch.all(cols[0, n_full:] == -7) and torch.all(cols[2, n_load:] == -7)             # nothing written past the counts
+    _check_against_oracle(mask_np, bm, bn, row_ptrs, cols, tiles, (n_full, n_part, n_load, nnz_elems))
 
 
 def test_static_compaction_equals_two_phase_on_consecutive_calls():
@@ -60,6 +75,37 @@ def test_static_compaction_equals_two_phase_on_consecutive_calls():
     _check_against_two_phase(a, 32, 32)
     _check_against_two_phase(c, 64, 16)
     _check_against_two_phase(c, 64, 16)
+
+
+def test_static_compaction_allocates_no_device_memory():
+    """What the entry point exists for: once a device has seen its first call, a call leaves the amount of free device
+    memory exactly as it found it.  The buffers are made before the measurement; the call itself goes straight to the
+    C ABI, so nothing of torch's caching allocator is involved either."""
+    from stof_b200 import _lib
+    L = _lib.lib()
+    mask_np = om.generate_causal_mask(1, 512).astype(np.float16)
+    mask_t = torch.from_numpy(mask_np).cuda()
+    bm = bn = 32
+    cap = (512 // bm) * (512 // bn)
+    _static_call(mask_t, bm, bn, cap, cap)                                   # first call on this device: the one-time set-up
+    dev = mask_t.device
+    row_ptrs = torch.empty(3, 512 // bm + 1, dtype=torch.int32, device=dev)
+    cols = torch.empty(3, cap, dtype=torch.int32, device=dev)
+    tiles = torch.empty(cap, bm, bn, dtype=torch.float16, device=dev)
+    counts = torch.empty(4, dtype=torch.int64, device=dev)
+    stream = _lib.current_stream_ptr(dev)
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info(dev)
+    reserved_before = torch.cuda.memory_reserved(dev)
+    for _ in range(2):
+        rc = L.stof_mask_compact_static(_lib.ptr(mask_t), _lib.STOF_DTYPE_F16, 1, 512, bm, bn, _lib.ptr(row_ptrs[0]), _lib.ptr(row_ptrs[1]),
+                                        _lib.ptr(row_ptrs[2]), _lib.ptr(cols[0]), _lib.ptr(cols[1]), _lib.ptr(cols[2]), cap, _lib.ptr(tiles),
+                                        cap, _lib.ptr(counts), stream)
+        assert rc == 0
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info(dev)
+    assert free_after == free_before and torch.cuda.memory_reserved(dev) == reserved_before
+    _check_against_oracle(mask_np, bm, bn, row_ptrs, cols, tiles, counts.tolist())
 
 
 def test_static_compaction_respects_capacities_and_limits():
