@@ -552,7 +552,7 @@ def encoder_measure(args, rank, world, local, steps, warmup):
     return {"metric": "BERT encoder tokens/s", "value": cfg.batch * cfg.seq_len / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
             "steps": steps, "warmup": warmup, "scaling": "strong", "workload": cfg.name, "global_batch": cfg.batch, "seq_len": cfg.seq_len,
             "layers": cfg.layers, "load_blocks": n_load, "tflops_all_gpus": tflops,
-            "frac_of_sustained_peak_per_gpu": tflops / world / peaks["tflops_sustained"], "gpu_launches": steps * cfg.layers * 7,
+            "frac_of_sustained_peak_per_gpu": tflops / world / peaks["tflops_sustained"], "gpu_launches": steps * cfg.layers * 6,
             "per_rank": [{"ms_per_step": float(t[0]), "sm_mhz_median": float(t[1]), "ms_x_ghz": float(t[0] * t[1] / 1e3)} for t in per_rank],
             "clocks": clocks.summary(), "parity_first_layer": parity}
 
@@ -630,12 +630,105 @@ def run_encoder(args, rank, world, local):
                      "kernel": "whole forward (GEMMs + attention + LayerNorm)"},
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": x_h.numel() * 2, "d2h_bytes_per_step": y_h.numel() * 2,
                 "ms_per_step": e2e_ms},
-        "gpu_launches": args.steps * cfg.layers * 7,
+        "gpu_launches": args.steps * cfg.layers * 6,
         "clocks": clocks.summary(),
         "graph_replay": {"ms_per_step": graph_ms, "value": tokens / (graph_ms * 1e-3), "unit": "tokens/s",
                          "note": "the same forward replayed as one CUDA graph (BertEncoder.capture)"},
     }
     print(json.dumps(line))
+    return 0
+
+
+def run_micro(args, local):
+    """Every kernel of the library once over, each on its own at a size where its roofline means something (inputs beyond L2
+    for the HBM-bound ones), timed with CUDA events over a loop; prints one JSON object.  This is also the command the ncu
+    summaries under profiles/ are taken from (`--only <name>` runs a single entry a few times)."""
+    import stof_b200
+    from stof_b200 import _lib, workloads as wl
+    dev = torch.device("cuda", local)
+    peaks = measured_peaks()
+    g = torch.Generator().manual_seed(7)
+    reps = max(args.steps, 1)
+
+    def rnd(*shape, scale=1.0):
+        return (torch.randn(*shape, generator=g) * scale).half().to(dev)
+
+    def timed(fn):
+        for _ in range(max(args.warmup, 1)):
+            fn()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        _lib.check_status(dev, "micro")
+        return e0.elapsed_time(e1) / reps
+
+    T = args.rows
+    out = {}
+
+    def gemm_entry(name, K, N, fn_name, extra=()):
+        a, w, b = rnd(T, K), rnd(K, N, scale=0.02), rnd(N)
+        y = torch.empty(T, N, dtype=torch.float16, device=dev)
+        r = rnd(T, N) if "residual" in fn_name else None
+        gam, bet = (rnd(N), rnd(N)) if "layernorm" in fn_name else (None, None)
+        f = getattr(stof_b200, fn_name)
+        if fn_name == "gemm_bias":
+            call = lambda: f(a, w, b, out=y)
+        elif fn_name == "gemm_bias_gelu":
+            call = lambda: f(a, w, b, "erf", out=y)
+        elif fn_name == "gemm_bias_residual":
+            call = lambda: f(a, w, b, r, out=y)
+        else:
+            call = lambda: f(a, w, b, r, gam, bet, 1e-12, out=y)
+        ms = timed(call)
+        tf = 2.0 * T * K * N / (ms * 1e-3) / 1e12
+        out[name] = {"rows": T, "k": K, "n": N, "us": ms * 1e3, "tflops": tf, "frac_of_burst_peak": tf / peaks["tflops"]}
+
+    def ln_entry(name, hidden, residual):
+        x = rnd(T, hidden)
+        r = rnd(T, hidden) if residual else None
+        gam, bet = rnd(hidden), rnd(hidden)
+        ms = timed(lambda: stof_b200.bias_residual_layernorm(x, None, r, gam, bet, 1e-12, out=x))
+        nbytes = T * hidden * 2 * (3 if residual else 2)
+        out[name] = {"rows": T, "hidden": hidden, "us": ms * 1e3, "gbs": nbytes / (ms * 1e-3) / 1e9,
+                     "frac_of_hbm_peak": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+
+    def compaction_entry(name, S):
+        mask = wl.expand_block_mask(wl.block_bigbird(S // 64, 1)).to(dev)
+        refresher = stof_b200.SparseStorageRefresher(mask, 64, 64)
+        ms = timed(refresher.refresh)
+        refresher.check()
+        out[name] = {"seq_len": S, "us": ms * 1e3, "gbs": mask.numel() * 2 / (ms * 1e-3) / 1e9,
+                     "frac_of_hbm_peak": mask.numel() * 2 / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "kernels": "classify_kernel + fill_bounded_kernel"}
+
+    entries = {
+        "gemm_qkv_1024": lambda: gemm_entry("gemm_qkv_1024", 1024, 3072, "gemm_bias"),
+        "gemm_outproj_residual_1024": lambda: gemm_entry("gemm_outproj_residual_1024", 1024, 1024, "gemm_bias_residual"),
+        "gemm_outproj_layernorm_1024": lambda: gemm_entry("gemm_outproj_layernorm_1024", 1024, 1024, "gemm_bias_residual_layernorm"),
+        "gemm_ffn1_gelu_1024": lambda: gemm_entry("gemm_ffn1_gelu_1024", 1024, 4096, "gemm_bias_gelu"),
+        "gemm_ffn2_residual_1024": lambda: gemm_entry("gemm_ffn2_residual_1024", 4096, 1024, "gemm_bias_residual"),
+        "gemm_ffn2_layernorm_1024": lambda: gemm_entry("gemm_ffn2_layernorm_1024", 4096, 1024, "gemm_bias_residual_layernorm"),
+        "gemm_outproj_layernorm_768": lambda: gemm_entry("gemm_outproj_layernorm_768", 768, 768, "gemm_bias_residual_layernorm"),
+        "gemm_one_block_small": lambda: gemm_entry("gemm_one_block_small", 768, 768, "gemm_bias"),
+        "layernorm_1024": lambda: ln_entry("layernorm_1024", 1024, False),
+        "layernorm_residual_1024": lambda: ln_entry("layernorm_residual_1024", 1024, True),
+        "layernorm_768": lambda: ln_entry("layernorm_768", 768, False),
+        "compaction_S2048": lambda: compaction_entry("compaction_S2048", 2048),
+        "compaction_S4096": lambda: compaction_entry("compaction_S4096", 4096),
+    }
+    for name, fn in entries.items():
+        if args.only and name not in args.only.split(","):
+            continue
+        if name == "gemm_one_block_small":
+            T_saved, T = T, 4096
+            fn()
+            T = T_saved
+        else:
+            fn()
+    print(json.dumps({"metric": "per-kernel timings", "rows": args.rows, "steps": reps, "peaks": peaks, "kernels": out}))
     return 0
 
 
@@ -645,7 +738,9 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="stof", choices=["stof", "reference"])
-    ap.add_argument("--workload", default="attention", choices=["attention", "encoder"])
+    ap.add_argument("--workload", default="attention", choices=["attention", "encoder", "micro"])
+    ap.add_argument("--rows", type=int, default=65536, help="micro: rows (tokens) of the GEMM / LayerNorm entries")
+    ap.add_argument("--only", default="", help="micro: comma-separated entry names to run (default: all)")
     ap.add_argument("--batch", type=int, default=0, help="override the batch size (profiling aid: smaller captures)")
     ap.add_argument("--no-encoder", action="store_true", help="skip the BERT-large encoder forward that the attention run reports under 'encoder'")
     ap.add_argument("--no-depth-report", action="store_true", help="skip the 24-layer parity figure of the encoder sub-record (a minute of CPU work)")
@@ -665,6 +760,8 @@ def main():
     try:
         if args.workload == "attention":
             return run_attention(args, rank, world, local)
+        if args.workload == "micro":
+            return run_micro(args, local) if rank == 0 else 0
         return run_encoder(args, rank, world, local)
     finally:
         if world > 1 and torch.distributed.is_initialized():

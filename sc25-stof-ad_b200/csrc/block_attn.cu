@@ -297,16 +297,28 @@ struct Item {
     int qt, head, batch, n;
     bool valid;
 };
-// Step one of fetching item k of this thread block: its raw number (A_NO_ITEM when the block has no k-th item).
-constexpr unsigned A_NO_ITEM = 0xffffffffu;
-__device__ __forceinline__ unsigned fetch_item_id(unsigned k, const AttnParams& p) {
+// Where this thread block's items come from: its stretch of the schedule table (read once), or the round-robin deal.
+struct ItemSource {
+    const int* ids;          // the block's item numbers in the caller's table (nullptr: default deal)
+    unsigned count;          // how many items the block has
+};
+__device__ __forceinline__ ItemSource item_source(const AttnParams& p) {
+    ItemSource src;
     if (p.schedule != nullptr) {
         const int b0 = __ldg(p.schedule + 1 + blockIdx.x), b1 = __ldg(p.schedule + 2 + blockIdx.x);
-        if (static_cast<long long>(k) >= static_cast<long long>(b1) - b0) return A_NO_ITEM;
-        return static_cast<unsigned>(__ldg(p.schedule + 2 + gridDim.x + b0 + static_cast<int>(k)));
+        src.ids = p.schedule + 2 + gridDim.x + b0;
+        src.count = b1 > b0 ? static_cast<unsigned>(b1 - b0) : 0u;
+    } else {
+        src.ids = nullptr;
+        src.count = blockIdx.x < p.total_items ? (p.total_items - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;
     }
-    const unsigned idx = blockIdx.x + k * gridDim.x;
-    return idx < p.total_items ? idx : A_NO_ITEM;
+    return src;
+}
+// Step one of fetching item k of this thread block: its raw number (A_NO_ITEM when the block has no k-th item).
+constexpr unsigned A_NO_ITEM = 0xffffffffu;
+__device__ __forceinline__ unsigned fetch_item_id(unsigned k, const ItemSource& src) {
+    if (k >= src.count) return A_NO_ITEM;
+    return src.ids != nullptr ? static_cast<unsigned>(__ldg(src.ids + k)) : blockIdx.x + k * gridDim.x;
 }
 // Step two: the item's coordinates and its tile count.
 __device__ __forceinline__ Item decode_item(unsigned id, const AttnParams& p, const int2* sched) {
@@ -341,9 +353,34 @@ __device__ __forceinline__ Item decode_item(unsigned id, const AttnParams& p, co
     it.head = static_cast<int>(bh - it.batch * p.heads);
     return it;
 }
-__device__ __forceinline__ Item fetch_item(unsigned k, const AttnParams& p, const int2* sched) {
-    return decode_item(fetch_item_id(k, p), p, sched);
+__device__ __forceinline__ Item fetch_item(unsigned k, const ItemSource& src, const AttnParams& p, const int2* sched) {
+    return decode_item(fetch_item_id(k, src), p, sched);
 }
+// The items of a thread block in order, fetched ahead of use: an item's number is requested two items early and decoded (which
+// asks for its step count) one item early, so that moving on to the next item waits for no load.  Items without steps are
+// skipped by the callers that only deal with steps (`skip_empty`).
+struct ItemQueue {
+    ItemSource src;
+    unsigned k;              // index of `cur` among the block's items
+    Item cur, nxt;
+    unsigned id2;
+    __device__ __forceinline__ void init(const AttnParams& p, const int2* sched) {
+        src = item_source(p);
+        k = 0;
+        cur = fetch_item(0, src, p, sched);
+        nxt = fetch_item(1, src, p, sched);
+        id2 = fetch_item_id(2, src);
+    }
+    __device__ __forceinline__ void pop(const AttnParams& p, const int2* sched) {
+        ++k;
+        cur = nxt;
+        nxt = decode_item(id2, p, sched);
+        id2 = fetch_item_id(k + 2, src);
+    }
+    __device__ __forceinline__ void skip_empty(const AttnParams& p, const int2* sched) {
+        while (cur.valid && cur.n == 0) pop(p, sched);
+    }
+};
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float d;
@@ -519,20 +556,21 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 // of the V loads, in the order the MMA warp consumes them.  `it` counts the items with steps (Q buffers alternate).
                 // A step takes one ring slot when both halves work on the same tile (or one of them has none), else two: first
                 // the tile of half A, then the tile of half B; all of a step's bytes are reported to the step's one barrier.
-                struct Cursor { unsigned k; Item item; int j, it; };
+                // (the step word of a cursor's position is requested when the cursor gets there, a step before it is needed)
+                struct Cursor { ItemQueue q; Item item; int j, it; uint32_t word; };
                 auto settle = [&](Cursor& c) {
-                    for (;;) {
-                        c.item = fetch_item(c.k, p, plan_sched);
-                        if (!c.item.valid || c.item.n > 0) return;
-                        ++c.k;
-                    }
+                    c.q.skip_empty(p, plan_sched);
+                    c.item = c.q.cur;
+                    if (c.item.valid) c.word = __ldg(plan_steps + static_cast<size_t>(c.item.qt) * p.max_steps);
                 };
                 auto advance = [&](Cursor& c) {
-                    if (++c.j >= c.item.n) { c.j = 0; ++c.k; ++c.it; settle(c); }
+                    if (++c.j >= c.item.n) { c.j = 0; ++c.it; c.q.pop(p, plan_sched); settle(c); }
+                    else c.word = __ldg(plan_steps + static_cast<size_t>(c.item.qt) * p.max_steps + c.j);
                 };
-                auto step_word = [&](const Cursor& c) { return __ldg(plan_steps + static_cast<size_t>(c.item.qt) * p.max_steps + c.j); };
+                auto step_word = [&](const Cursor& c) { return c.word; };
                 Cursor kc, vc;
-                kc.k = 0; kc.j = 0; kc.it = 0;
+                kc.q.init(p, plan_sched);
+                kc.j = 0; kc.it = 0; kc.word = 0;
                 settle(kc);
                 vc = kc;
                 unsigned uk = 0, uv = 0;                      // ring slots used so far
@@ -606,24 +644,21 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 const uint64_t v_desc0 = make_smem_desc_sw128(smem_u32(v_smem), 16, 1024);
                 // two cursors over the same stream of steps: the QK^T cursor runs A_SBUF steps ahead of the PV cursor.  The step
                 // word of a cursor's position is requested as soon as the cursor gets there, a whole step before it is needed.
-                struct Cursor { unsigned k; int qt, n, j, it; bool valid; uint32_t word; };
+                struct Cursor { ItemQueue q; int qt, n, j, it; bool valid; uint32_t word; };
                 auto settle = [&](Cursor& c) {
-                    for (;;) {
-                        const Item item = fetch_item(c.k, p, plan_sched);
-                        c.valid = item.valid;
-                        c.n = item.n;
-                        c.qt = item.qt;
-                        if (!item.valid || item.n > 0) break;
-                        ++c.k;
-                    }
+                    c.q.skip_empty(p, plan_sched);
+                    c.valid = c.q.cur.valid;
+                    c.n = c.q.cur.n;
+                    c.qt = c.q.cur.qt;
                     if (c.valid) c.word = __ldg(plan_steps + static_cast<size_t>(c.qt) * p.max_steps);
                 };
                 auto advance = [&](Cursor& c) {
-                    if (++c.j >= c.n) { c.j = 0; ++c.k; ++c.it; settle(c); }
+                    if (++c.j >= c.n) { c.j = 0; ++c.it; c.q.pop(p, plan_sched); settle(c); }
                     else c.word = __ldg(plan_steps + static_cast<size_t>(c.qt) * p.max_steps + c.j);
                 };
                 Cursor qk, pv;
-                qk.k = 0; qk.j = 0; qk.it = 0; qk.word = 0;
+                qk.q.init(p, plan_sched);
+                qk.j = 0; qk.it = 0; qk.word = 0;
                 settle(qk);
                 pv = qk;
                 unsigned gq = 0, g = 0;                       // steps issued: QK^T, PV
@@ -663,6 +698,7 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 for (int i = 0; i < A_SBUF && qk.valid; ++i) issue_qk();
                 while (pv.valid) {
                     if (pv.j == 0) mbar_wait(&bars[AB_O_FREE], static_cast<uint32_t>((pv.it & 1) ^ 1), wctx, AB_O_FREE);     // the previous item's O was read
+                    const uint32_t o_tmem = tmem_base + A_COL_O;
                     const uint32_t w = pv.word;
                     const unsigned ta = w & 0xFFFFu, tb = w >> 16;
                     const bool two = ta != A_NO_TILE && tb != A_NO_TILE && ta != tb;
@@ -677,11 +713,11 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     // a half's steps are the first ones of the item, so its first product (which overwrites O) comes at step 0
                     const uint64_t vd0 = v_desc0 + static_cast<uint64_t>(sl0 * (A_KV_BYTES >> 4));
                     if (ta == tb) {
-                        mma_chain_pv(tmem_base + A_COL_O, p_tmem, vd0, idesc_pv2, acc);
+                        mma_chain_pv(o_tmem, p_tmem, vd0, idesc_pv2, acc);
                     } else {
-                        if (ta != A_NO_TILE) mma_chain_pv(tmem_base + A_COL_O, p_tmem, vd0, idesc_pv, acc);
+                        if (ta != A_NO_TILE) mma_chain_pv(o_tmem, p_tmem, vd0, idesc_pv, acc);
                         if (tb != A_NO_TILE)
-                            mma_chain_pv(tmem_base + A_COL_O + A_LANE_B, p_tmem + A_LANE_B,
+                            mma_chain_pv(o_tmem + A_LANE_B, p_tmem + A_LANE_B,
                                          two ? v_desc0 + static_cast<uint64_t>(sl1 * (A_KV_BYTES >> 4)) : vd0, idesc_pv, acc);
                     }
                     tc_commit(&bars[AB_V_EMPTY + sl0]);
@@ -733,31 +769,37 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     tma_store_commit();
                 }
             };
-            // two-deep item pipeline: the schedule entry and half row of item k+2 and the row-dependent loads of item k+1 are
-            // in flight while item k is processed
-            Item item = fetch_item(0, p, plan_sched);
-            Item item2 = fetch_item(1, p, plan_sched);
-            int half_next = item_half(item), half2 = item_half(item2);
-            int part_base_next = item_row_base(item, half_next);
-            uint2 cw_next = (item.valid && item.n > 0) ? __ldg(item_codes(item)) : make_uint2(0u, 0u);
-            for (unsigned k = 0; item.valid; ++k) {
-                const Item cur_item = item;
-                const int part_base = part_base_next;
-                uint2 cw = cw_next;                              // codes of step 0
-                const int half_row = half_next;
-                item = item2;
-                half_next = half2;
-                part_base_next = item_row_base(item, half_next);
-                cw_next = (item.valid && item.n > 0) ? __ldg(item_codes(item)) : make_uint2(0u, 0u);
-                item2 = fetch_item(k + 2, p, plan_sched);
-                half2 = item_half(item2);
-
+            // two-deep item pipeline: what items k+1 and k+2 need from global memory (schedule entry, step count, half rows, row
+            // pointer, first codes: chains of dependent loads) is requested while item k waits for its last PV product
+            const ItemSource isrc = item_source(p);
+            Item cur_item = fetch_item(0, isrc, p, plan_sched);
+            Item item1 = fetch_item(1, isrc, p, plan_sched);
+            int half_row = item_half(cur_item), half1 = item_half(item1);
+            int part_base = item_row_base(cur_item, half_row);
+            uint2 cw = (cur_item.valid && cur_item.n > 0) ? __ldg(item_codes(cur_item)) : make_uint2(0u, 0u);      // codes of step 0
+            for (unsigned k = 0; cur_item.valid; ++k) {
+                // the values of the items after this one; they replace the current ones at the end of the iteration
+                Item item2;
+                int half2, part_base1;
+                uint2 cw1;
+                auto fetch_ahead = [&]() {
+                    part_base1 = item_row_base(item1, half1);
+                    cw1 = (item1.valid && item1.n > 0) ? __ldg(item_codes(item1)) : make_uint2(0u, 0u);
+                    item2 = fetch_item(k + 2, isrc, p, plan_sched);
+                    half2 = item_half(item2);
+                };
+                auto rotate = [&]() {
+                    cur_item = item1; half_row = half1; part_base = part_base1; cw = cw1;
+                    item1 = item2; half1 = half2;
+                };
                 const int n = cur_item.n;
                 if (n == 0) {
                     uint4 z[8];
 #pragma unroll
                     for (int c = 0; c < 8; ++c) z[c] = make_uint4(0u, 0u, 0u, 0u);
                     store_rows(z, cur_item, half_row);
+                    fetch_ahead();
+                    rotate();
                     continue;
                 }
                 const uint2* my_codes = item_codes(cur_item);
@@ -857,6 +899,7 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     if (lane == 0) mbar_arrive(&bars[AB_P_FULL + b]);
                 }
                 // ---------------------------------------------------------- item epilogue: O / l -> fp16 -> global
+                fetch_ahead();                                  // the loads for the next items overlap the wait for the last PV product
                 {
                     const int pb = static_cast<int>((g - 1) % A_SBUF);
                     mbar_wait(&bars[AB_PV_DONE + pb], ((g - 1) / A_SBUF) & 1, wctx, AB_PV_DONE + pb);
@@ -884,6 +927,7 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                         store_rows(u, cur_item, half_row);
                     }
                 }
+                rotate();
             }
             if ((lane & 15) == 0) tma_store_wait_all();      // every output store of this warp has been performed
         }
