@@ -37,9 +37,24 @@ constexpr size_t WS_HEADER = 16;
 
 __host__ __device__ inline size_t cls_bytes(int nbm, int nbn) { return (static_cast<size_t>(nbm) * nbn + 15) & ~static_cast<size_t>(15); }
 
-// flags for one 16-byte chunk: bit0 = some element != 1, bit1 = some element != 0; also the non-zero count
+// flags for one 16-byte chunk: bit0 = some element != 1, bit1 = some element != 0; also the non-zero count.
+// Masks are made of runs of equal values, so nearly every chunk is eight ones or eight zeros: both cases are settled on the
+// whole chunk with a handful of word operations (AND / OR of the four words against the bit pattern of 1.0, sign bits ignored
+// for zero: -0.0 == 0), and only a mixed chunk is looked at element by element.
 template <bool F32>
 __device__ __forceinline__ void chunk_flags(const uint4& v, unsigned& flags, unsigned& nz) {
+    constexpr unsigned ONE = F32 ? 0x3F800000u : 0x3C003C00u;
+    constexpr unsigned MAG = F32 ? 0x7FFFFFFFu : 0x7FFF7FFFu;
+    const unsigned all_and = v.x & v.y & v.z & v.w, all_or = v.x | v.y | v.z | v.w;
+    if (all_and == ONE && all_or == ONE) {                 // every element is exactly 1.0
+        flags |= 2u;
+        nz += F32 ? 4u : 8u;
+        return;
+    }
+    if ((all_or & MAG) == 0u) {                            // every element is +0.0 or -0.0
+        flags |= 1u;
+        return;
+    }
     const unsigned w[4] = {v.x, v.y, v.z, v.w};
     if (F32) {
 #pragma unroll
@@ -139,21 +154,33 @@ classify_kernel(const void* __restrict__ mask, int seq_len, int bm, int bn, int 
     const int chunks_per_row = cols / EPC;
     const int total = bm * chunks_per_row;
     unsigned nz = 0;
-    // four independent 16-byte loads in flight per thread before any of them is consumed
+    // four independent 16-byte loads in flight per thread before any of them is consumed.  Chunk idx of the block's
+    // bm x chunks_per_row grid lies at (row, chunk) = (idx / chunks_per_row, idx % chunks_per_row); the four positions of a
+    // thread advance by a fixed (rows, chunks) step per iteration, so the division is done once, outside the loop.
     constexpr int BATCH = 4;
-    for (int idx0 = threadIdx.x; idx0 < total; idx0 += BATCH * blockDim.x) {
+    const int step = BATCH * blockDim.x;
+    const int step_r = step / chunks_per_row, step_c = step - step_r * chunks_per_row;
+    int pr[BATCH], pc[BATCH];
+#pragma unroll
+    for (int u = 0; u < BATCH; ++u) {
+        const int idx = threadIdx.x + u * blockDim.x;
+        pr[u] = idx / chunks_per_row;
+        pc[u] = idx - pr[u] * chunks_per_row;
+    }
+    for (int idx0 = threadIdx.x; idx0 < total; idx0 += step) {
         uint4 v[BATCH];
         int tile_of[BATCH];
 #pragma unroll
         for (int u = 0; u < BATCH; ++u) {
-            const int idx = idx0 + u * blockDim.x;
-            if (idx < total) {
-                const int r = idx / chunks_per_row, cc = idx - r * chunks_per_row;
-                v[u] = __ldg(reinterpret_cast<const uint4*>(base + (static_cast<size_t>(r) * seq_len + cc * EPC) * elem_bytes));
-                tile_of[u] = (cc * EPC) / bn;
+            if (idx0 + u * static_cast<int>(blockDim.x) < total) {
+                v[u] = __ldg(reinterpret_cast<const uint4*>(base + (static_cast<size_t>(pr[u]) * seq_len + pc[u] * EPC) * elem_bytes));
+                tile_of[u] = (pc[u] * EPC) / bn;
             } else {
                 tile_of[u] = -1;
             }
+            pr[u] += step_r;
+            pc[u] += step_c;
+            if (pc[u] >= chunks_per_row) { pc[u] -= chunks_per_row; ++pr[u]; }
         }
 #pragma unroll
         for (int u = 0; u < BATCH; ++u) {
