@@ -26,6 +26,7 @@
 //               2^8), P written with tcgen05.st, final O / l normalisation staged in shared memory and written with TMA stores
 // With three S buffers the QK^T products run ahead of the softmax warps.  Masking of partial tiles and the rescale of O are
 // out-of-line functions that work on tensor memory in place.  Tiles nobody lists are never loaded.
+#include <atomic>
 #include "stof_host.h"
 #include "stof_ptx.cuh"
 
@@ -1018,7 +1019,7 @@ static int launch_plan(const int* full_row_ptr, const int* full_col_idx, const i
     STOF_CUDA(cudaMemsetAsync(pl, 0, sizeof(PlanHeader), stream));
     STOF_CUDA(cudaMemsetAsync(ticket, 0, 16, stream));
     const size_t smem = plan_table_bytes(seq_len, block_m, block_n);
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64];     // per device; host threads may race here, every one of them stores the same value
     int dev = 0;
     STOF_CUDA(cudaGetDevice(&dev));
     if (smem > 40 * 1024 && (dev < 0 || dev >= 64 || !configured[dev])) {
@@ -1090,7 +1091,7 @@ static int launch_block_attn(const void* q, const void* k, const void* v, void* 
     if (int rc = make_qkv_map(&mk, k, batch, heads, seq_len, k_strides, A_TKV, &p.slot_s[1], &p.slot_h[1], &p.slot_b[1])) return rc;
     if (int rc = make_qkv_map(&mv, v, batch, heads, seq_len, v_strides, A_TKV, &p.slot_s[2], &p.slot_h[2], &p.slot_b[2])) return rc;
 
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64];     // per device; host threads may race here, every one of them stores the same value
     int dev = 0;
     STOF_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {

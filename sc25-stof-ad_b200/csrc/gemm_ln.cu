@@ -22,6 +22,7 @@
 // finished reading the partials of row block t.
 // All blocks of a cluster meet at a cluster barrier before they leave: nobody frees shared memory a peer may still write.
 #include <cstdlib>
+#include <atomic>
 #include "stof_host.h"
 #include "stof_ptx.cuh"
 
@@ -362,7 +363,7 @@ extern "C" int stof_gemm_bias_residual_layernorm(const void* a, long long lda, c
         const uint32_t box[2] = {64, 32};
         if (int rc = make_tensor_map_f16(&mc, c, 2, dims, strides, box)) return rc;
     }
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64];     // per device; host threads may race here, every one of them stores the same value
     int dev = 0;
     STOF_CUDA(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !configured[dev]) {

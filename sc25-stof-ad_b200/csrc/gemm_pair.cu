@@ -13,6 +13,7 @@
 //               leader's barrier with remote mbarrier arrives
 // Every copy and every commit names exactly one block's barrier.  Both blocks meet at a cluster barrier before they leave, so
 // that neither frees shared or tensor memory its peer may still signal, read or write.
+#include <atomic>
 #include "stof_host.h"
 #include "stof_ptx.cuh"
 #include "stof_epilogue.cuh"
@@ -275,7 +276,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 template <int EPI>
 int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mc, const __half* bias, const __half* residual, long long ldr,
                 int m, int n, int k, int* status, cudaStream_t stream) {
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64];     // per device; host threads may race here, every one of them stores the same value
     int dev = 0;
     STOF_CUDA(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !configured[dev]) {

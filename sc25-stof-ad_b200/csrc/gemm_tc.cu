@@ -11,6 +11,7 @@
 // Weights are consumed in their (K, N) row-major layout through an MN-major shared-memory
 // descriptor, so no transposed copy is ever made.
 #include <cstdlib>
+#include <atomic>
 #include "stof_host.h"
 #include "stof_ptx.cuh"
 #include "stof_epilogue.cuh"
@@ -232,7 +233,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 template <int EPI>
 int launch(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mc, const __half* bias, const __half* residual, long long ldr,
            int m, int n, int k, int* status, cudaStream_t stream) {
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64];     // per device; host threads may race here, every one of them stores the same value
     int dev = 0;
     STOF_CUDA(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !configured[dev]) {

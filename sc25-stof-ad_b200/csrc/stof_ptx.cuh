@@ -76,7 +76,20 @@ struct WaitCtx {
     int* status_gmem;           // device status word (may be nullptr)
 };
 
+// Non-blocking probe of the phase: for a barrier that has completed already this is cheaper than try_wait, which may suspend.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred P;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, int barrier_id) {
+    if (mbar_test_wait(bar, parity)) return;             // the common case on the paths that run ahead: nothing to wait for
     if (mbar_try_wait(bar, parity)) return;
     const long long t0 = clock64();
     int spins = 0;

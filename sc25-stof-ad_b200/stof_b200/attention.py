@@ -130,8 +130,7 @@ def attention_plan(full_row_ptr, full_col_idx, part_row_ptr, part_col_idx, seq_l
     once and re-plans with `pair_halves` when that spares tile steps (an index used once is not worth the host read);
     "eager" does so at once, "off" never."""
     tensors = (full_row_ptr, full_col_idx, part_row_ptr, part_col_idx)
-    key = tuple((t.data_ptr(), t._version, t.numel(), _INDEX_GENERATION.get(t.data_ptr(), 0)) for t in tensors) + \
-        (seq_len, block_m, block_n, str(full_row_ptr.device))
+    key = _plan_key(tensors, seq_len, block_m, block_n)
     hit = _PLAN_CACHE.get(key)
     if hit is not None:
         _PLAN_CACHE.move_to_end(key)
@@ -150,6 +149,13 @@ def attention_plan(full_row_ptr, full_col_idx, part_row_ptr, part_col_idx, seq_l
         plan = _build_plan(tensors, pairs, seq_len, block_m, block_n)
     _HOT_PLANS.add(plan.data_ptr())
     return _cache_plan(key, plan, tensors, True)
+
+
+def _plan_key(tensors, seq_len, block_m, block_n):
+    """Identity of a block index for the plan cache: storage address, torch's version counter, length and the generation that
+    `index_rewritten` advances for writes torch does not see."""
+    return tuple((t.data_ptr(), t._version, t.numel(), _INDEX_GENERATION.get(t.data_ptr(), 0)) for t in tensors) + \
+        (seq_len, block_m, block_n, str(tensors[0].device))
 
 
 def _cache_plan(key, plan, tensors, decided):

@@ -226,6 +226,21 @@ def test_pair_halves_host_logic():
     assert all(a % 2 == b % 2 for a, b in pairs)
 
 
+def test_plan_cache_key_follows_in_place_rewrites():
+    """The plan cache identifies a block index by its tensors' storage, version and length; a rewrite through the C ABI moves
+    none of them, so `index_rewritten` advances a generation that is part of the key (the refresher calls it)."""
+    from stof_b200 import attention as A
+    idx = tuple(torch.zeros(n, dtype=torch.int32) for n in (5, 7, 5, 3))
+    k0 = A._plan_key(idx, 256, 64, 64)
+    assert A._plan_key(idx, 256, 64, 64) == k0
+    A.index_rewritten(idx[1], None)
+    k1 = A._plan_key(idx, 256, 64, 64)
+    assert k1 != k0 and k1[0] == k0[0] and k1[1] != k0[1]
+    idx[0].add_(1)                                       # a write torch does see moves the version counter
+    assert A._plan_key(idx, 256, 64, 64) != k1
+    assert A._plan_key(idx, 256, 32, 64) != A._plan_key(idx, 256, 64, 64)
+
+
 def test_operator_selector_host_logic():
     """The selector keeps the reference's interface (src/benchmk_attn_unified.py:100-163) and result format; on this
     kernel it never answers "row-wise" and picks the index granularity from whether partial blocks exist."""
