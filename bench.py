@@ -722,6 +722,7 @@ def run_micro(args, local):
         "gemm_ffn1_gelu_1024": lambda: gemm_entry("gemm_ffn1_gelu_1024", 1024, 4096, "gemm_bias_gelu"),
         "gemm_ffn2_residual_1024": lambda: gemm_entry("gemm_ffn2_residual_1024", 4096, 1024, "gemm_bias_residual"),
         "gemm_ffn2_layernorm_1024": lambda: gemm_entry("gemm_ffn2_layernorm_1024", 4096, 1024, "gemm_bias_residual_layernorm"),
+        "gemm_outproj_residual_768": lambda: gemm_entry("gemm_outproj_residual_768", 768, 768, "gemm_bias_residual"),
         "gemm_outproj_layernorm_768": lambda: gemm_entry("gemm_outproj_layernorm_768", 768, 768, "gemm_bias_residual_layernorm"),
         "gemm_one_block_small": lambda: gemm_entry("gemm_one_block_small", 768, 768, "gemm_bias"),
         "layernorm_1024": lambda: ln_entry("layernorm_1024", 1024, False),

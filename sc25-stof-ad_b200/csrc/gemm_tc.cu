@@ -305,12 +305,15 @@ extern "C" int stof_gemm_bias_act(const void* a, long long lda, const void* w, l
     }
     const __half *bp = static_cast<const __half*>(bias), *rp = static_cast<const __half*>(residual);
     {
-        // pairs of blocks on 256 x 256 tiles once every pair of SMs gets at least two of them; small problems keep 128 x 256 tiles
+        // pairs of blocks on 256 x 256 tiles once every pair of SMs gets at least two of them; small problems keep 128 x 256 tiles.
+        // The residual epilogue at K <= 1024 outlasts the main loop in both kernels; measured per shape (K = N = 1024 and 768,
+        // bias + residual): 16384 rows one-block +3 %, 65536 rows equal within 1.5 %, 262144 rows two-block +3 % - so that case
+        // moves to the two-block kernel only from 16 tiles per pair of SMs on.
         const long long tiles256 = static_cast<long long>((m + 255) / 256) * ((n + 255) / 256);
         const int mode = pair_mode();
-        // (the residual epilogue outlasts a main loop of K <= 1024 in both kernels; there the one-block kernel's shorter tiles win)
+        const long long pairs = sm_count() / 2;
         const bool short_residual = epilogue == STOF_EPI_BIAS_RESIDUAL && k <= 1024;
-        if (mode == 1 || (mode < 0 && !short_residual && tiles256 >= 2LL * (sm_count() / 2)))
+        if (mode == 1 || (mode < 0 && tiles256 >= (short_residual ? 16LL : 2LL) * pairs))
             return gemm_pair_dispatch(ma, mw, mc, bp, rp, ldr, m, n, k, epilogue, status_dev, stream);
     }
     switch (epilogue) {
