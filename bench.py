@@ -113,7 +113,7 @@ def attention_config_dict(cfg, n_load_blocks, flops, parallelism):
 # entry), with the batch that capture ran at: every (batch, head) pair is an independent set of work items, so the traffic
 # of a launch grows in proportion to the batch.
 NCU_TRAFFIC = {
-    "mha_bigbird_b16_h12_s2048": {"bytes": 89.26e6, "batch": 8, "profile": "profiles/block_attn_kernel_cfg2_batch8.md"},
+    "mha_bigbird_b16_h12_s2048": {"bytes": 86.25e6, "batch": 8, "profile": "profiles/block_attn_kernel_cfg2_batch8.md"},
 }
 
 
