@@ -101,15 +101,18 @@ int stof_mask_compact_static(const void* mask, int mask_dtype, int batch, int se
  *           block_attn_mask_gpu, src/ops/src/block_attn_mask.cpp:17-49.
  *
  * Two calls.  stof_block_attn_plan turns the block index (the full_* and part_* lists of
- * get_sparse_storage) into the kernel's own 128 x 64 tiling: per 128-row query tile the ordered list
- * of 64-wide key tiles that any of its row blocks lists, a code per 16 x 16 group (absent / full /
- * partial tile i) and the order in which the scheduler visits the query tiles.  It depends on the
- * index only, so one plan serves every call with that index (every layer of an encoder).  The plan
- * buffer is caller-owned scratch of stof_block_attn_plan_bytes() bytes.
+ * get_sparse_storage) into the kernel's own tiling.  A work item is a pair of 64-row halves of the
+ * sequence (halves 2t and 2t + 1), each of which walks its own list of 64-wide key tiles - the tiles any
+ * of its row blocks lists; the plan lays the two lists out step by step (tiles both halves list share a
+ * step), with a code per 16 x 16 group and step (absent / full / partial tile i) and the order in which
+ * the scheduler visits the items.  It depends on the index only, so one plan serves every call with that
+ * index (every layer of an encoder).  The plan buffer is caller-owned scratch of
+ * stof_block_attn_plan_bytes() bytes; the kernel checks that a plan was made for the sequence length and
+ * block shape it is launched with and reports another one through status_dev.
  * stof_block_attn runs the attention.  For each row block only the listed column blocks take part; a
  * partial block adds its fp16 tile to the unscaled scores before the softmax scale, as the reference
  * kernel does.  A row without any listed key yields zeros.  `out` may alias `q` (the reference
- * overwrites q): a query tile is read completely before its rows are written.
+ * overwrites q): an item's query rows are read completely before they are written.
  * Strides are in elements for (batch, head, row); the innermost (head_dim) stride is 1.  All base
  * pointers 16-byte aligned, strides multiples of 8 elements.  block_m, block_n in {16,32,64,128};
  * seq_len a multiple of both.  `num_warps` is accepted for signature compatibility and ignored.
@@ -121,15 +124,15 @@ int stof_block_attn_plan(const int* full_row_ptr, const int* full_col_idx,
                          int seq_len, int block_m, int block_n,
                          void* plan, size_t plan_bytes, int* status_dev, void* stream);
 
-/* The same plan with the query tiles put together by the caller.  No counterpart in the reference
- * (its kernel works on one BLOCK_M row block per thread block).  The kernel's 128-row query tile is
- * two 64-row halves of the sequence, halves 2t and 2t + 1 in the plan above.  Here `pairs` (device,
- * 2 ints per query tile, ceil(seq_len / 128) tiles) names the two halves of every tile by their index
- * seq_row / 64; the second may be -1.  A caller pairs halves whose lists of key tiles agree (rows r
- * and r + 2 of a dilated mask, say), which spares the tensor core and half of the softmax warps the
- * key tiles that only one half of a default tile lists.  Every half must appear in exactly one tile:
- * a half that is left out is never written, which the plan does not check; an index outside
- * [0, ceil(seq_len / 64)) sets *status_dev and the tile falls back to half 0 alone. */
+/* The same plan with the work items put together by the caller.  No counterpart in the reference
+ * (its kernel works on one BLOCK_M row block per thread block).  Here `pairs` (device, 2 ints per item,
+ * ceil(seq_len / 128) items) names the two 64-row halves of every item by their index seq_row / 64; the
+ * second may be -1.  The two halves of an item work side by side, each on its own key tiles, so an item
+ * takes as many steps as its longer list and loads every tile either half lists: a caller pairs halves
+ * with equally long lists and, among those, halves whose lists agree (rows r and r + 2 of a dilated
+ * mask, say).  Every half must appear in exactly one item: a half that is left out is never written,
+ * which the plan does not check; an index outside [0, ceil(seq_len / 64)) sets *status_dev and the item
+ * falls back to half 0 alone. */
 int stof_block_attn_plan_paired(const int* full_row_ptr, const int* full_col_idx,
                                 const int* part_row_ptr, const int* part_col_idx, const int* pairs,
                                 int seq_len, int block_m, int block_n,
@@ -145,13 +148,13 @@ int stof_block_attn(const void* q, const void* k, const void* v, void* out,
 
 /* stof_block_attn with the deal of the work items to the thread blocks given by the caller.  No counterpart in the
  * reference (its kernels take one 64-row block per thread block from the launch grid,
- * src/ops/src/block_attn_mask_cuda.cu:6026-6316); here the kernel is persistent and a work item is one 128-row query tile
- * of one (batch, head).  By default the items are dealt round-robin, heaviest tiles first; query tiles with very different
- * tile counts then leave some blocks with up to 10-20 % more steps than the average.  `schedule` (device, int32) lets the
- * host balance them, e.g. by a longest-processing-time assignment over the per-tile counts that the plan holds
+ * src/ops/src/block_attn_mask_cuda.cu:6026-6316); here the kernel is persistent and a work item is one pair of 64-row halves
+ * of one (batch, head).  By default the items are dealt round-robin, heaviest first; items with very different step counts
+ * then leave some blocks with up to 10-20 % more steps than the average.  `schedule` (device, int32) lets the host balance
+ * them, e.g. by a longest-processing-time assignment over the per-item step counts that the plan holds
  * (stof_b200/attention.py: attention_schedule):
  *   schedule[0] = G (thread blocks, 1 <= G <= 2 x SMs), schedule[1 .. G + 1] = offsets, then the item ids,
- *   id = (batch_index * heads + head_index) * ceil(seq_len / 128) + query_tile; block b works through
+ *   id = (batch_index * heads + head_index) * ceil(seq_len / 128) + item_of_the_plan; block b works through
  *   ids[offset[b] .. offset[b + 1]) in that order.  Every item must appear exactly once (items left out are not computed).
  * `schedule_blocks` repeats G for validation on the host. */
 int stof_block_attn_scheduled(const void* q, const void* k, const void* v, void* out,
@@ -174,8 +177,9 @@ int stof_block_attn_scheduled(const void* q, const void* k, const void* v, void*
  * (max(x, 0): the FFN activation of the T5 loops, src/benchmk_end2end.py:203,313).
  * bias may be NULL.
  * Two kernels serve the call: shapes with at least two 256 x 256 tiles per pair of multiprocessors run on
- * pairs of thread blocks (tcgen05 cta_group::2, clusters of two), smaller ones and residual epilogues with
- * K <= 1024 on single blocks with 128 x 256 tiles; the results agree within fp16 rounding.  The
+ * pairs of thread blocks (tcgen05 cta_group::2, clusters of two), smaller ones - and residual epilogues with
+ * K <= 1024 below 16 such tiles per pair - on single blocks with 128 x 256 tiles; the results agree within
+ * fp16 rounding.  The
  * environment variable STOF_B200_GEMM_PAIR = 0 / 1, read once per process, forces one of the two
  * (a testing aid).  GELU_ERF evaluates x * Phi(x) with a polynomial (|error| < 1.1e-4).
  * ------------------------------------------------------------------------------------------ */
