@@ -386,15 +386,15 @@ extern "C" int stof_gemm_bias_residual_layernorm(const void* a, long long lda, c
     cfg.numAttrs = 1;
     // persistent: exactly as many clusters as the GPU keeps resident at once (the SMs of a cluster lie in one processing
     // cluster of the chip, so fewer than SMs / cluster size may fit), cached per device and cluster size
-    static int resident[64][L_MAX_CLUSTER + 1] = {};
-    int clusters = (dev >= 0 && dev < 64) ? resident[dev][cluster] : 0;
+    static std::atomic<int> resident[64][L_MAX_CLUSTER + 1];
+    int clusters = (dev >= 0 && dev < 64) ? resident[dev][cluster].load() : 0;
     if (clusters == 0) {
         STOF_CUDA(cudaOccupancyMaxActiveClusters(&clusters, gemm_ln_kernel, &cfg));
         if (clusters < 1) {
             set_error("gemm+layernorm: no cluster of %d thread blocks fits on this GPU", cluster);
             return STOF_E_LIMIT;
         }
-        if (dev >= 0 && dev < 64) resident[dev][cluster] = clusters;
+        if (dev >= 0 && dev < 64) resident[dev][cluster].store(clusters);
     }
     if (clusters > tiles_m) clusters = tiles_m;
     cfg.gridDim = dim3(static_cast<unsigned>(clusters * cluster));
