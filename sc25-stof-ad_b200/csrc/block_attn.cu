@@ -770,11 +770,13 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     tma_store_commit();
                 }
             };
-            // two-deep item pipeline: what items k+1 and k+2 need from global memory (schedule entry, step count, half rows, row
-            // pointer, first codes: chains of dependent loads) is requested while item k waits for its last PV product
+            // item pipeline: what items k+1 and k+2 need from global memory (step count, half rows, row pointer, first codes:
+            // chains of dependent loads) is requested while item k waits for its last PV product, and the schedule entry that
+            // names item k+3 with it, so that decoding an item never waits for its number
             const ItemSource isrc = item_source(p);
             Item cur_item = fetch_item(0, isrc, p, plan_sched);
             Item item1 = fetch_item(1, isrc, p, plan_sched);
+            unsigned id_ahead = fetch_item_id(2, isrc);      // number of item k + 2, requested an item before it is decoded
             int half_row = item_half(cur_item), half1 = item_half(item1);
             int part_base = item_row_base(cur_item, half_row);
             uint2 cw = (cur_item.valid && cur_item.n > 0) ? __ldg(item_codes(cur_item)) : make_uint2(0u, 0u);      // codes of step 0
@@ -786,7 +788,8 @@ block_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 auto fetch_ahead = [&]() {
                     part_base1 = item_row_base(item1, half1);
                     cw1 = (item1.valid && item1.n > 0) ? __ldg(item_codes(item1)) : make_uint2(0u, 0u);
-                    item2 = fetch_item(k + 2, isrc, p, plan_sched);
+                    item2 = decode_item(id_ahead, p, plan_sched);
+                    id_ahead = fetch_item_id(k + 3, isrc);
                     half2 = item_half(item2);
                 };
                 auto rotate = [&]() {
